@@ -1,0 +1,375 @@
+#!/usr/bin/env python
+"""Benchmark of the MoE routing-and-dispatch path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload c5] [--impl ours|reference]
+
+One "step" is one pass of the whole path (gate logits -> scoring/top-k ->
+histogram/scan -> row scatter [-> expert-parallel exchange at N > 1]) over one
+batch of seeded synthetic tokens.  Rank 0 prints ONE JSON line.
+
+* ``value``: routed tokens/s, whole job, inputs resident in HBM, device time
+  from CUDA events around every step on the launching stream (L2 flushed by a
+  256 MiB write between steps), max over ranks.
+* ``e2e``: the same metric through the public callable with HOST buffers:
+  pinned-host tokens copied in and every output copied back inside the timed
+  region.
+* ``roofline``: the row-scatter kernel (dominant), algorithmic bytes / its
+  device time, against the measured HBM copy bandwidth of this pool.
+* ``cpu_baseline`` / ``--impl reference``: the CPU oracle (a port of the
+  reference's algorithm; the reference has no CPU implementation of this path)
+  on the box's host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path[:0] = [str(ROOT), str(ROOT / "ernie-evolve-results_b200")]
+
+METRIC = "routed_tokens_per_s"
+UNIT = "tokens/s"
+FALLBACK_HBM_GBS = 6650.0
+
+
+def env_int(name, default):
+    try:
+        return int(os.environ.get(name, default))
+    except ValueError:
+        return default
+
+
+def measured_hbm_peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    try:
+        return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [v.strip() for v in ln.split(",")]
+            if len(f) < 7:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def session_kwargs(kw):
+    out = {k: v for k, v in kw.items() if k in ("score_fn", "bias_mode", "n_groups", "topk_groups", "group_topk",
+                                                  "renorm", "routed_scale", "norm_min", "capacity", "rows_format",
+                                                  "w_layout")}
+    return out
+
+
+def cpu_pass(tensors, kw, ranks=1, E=None):
+    """One full pass of the path on the CPU oracle (all ranks' tokens; EP exchange simulated for ranks > 1)."""
+    from oracle import cpu_oracle
+    from moe_rd import workloads
+    import numpy as np
+    import torch
+
+    def bits(t):
+        return t.contiguous().view(torch.int16).numpy().view(np.uint16)
+
+    per = []
+    for r in range(ranks):
+        t = tensors[r]
+        w = t["w"].numpy() if t["w"].dtype == torch.float32 else bits(t["w"])
+        per.append(cpu_oracle.route_dispatch(bits(t["x"]), w, **workloads.oracle_kwargs(kw, t["bias"])))
+    if ranks > 1:
+        cpu_oracle.ep_exchange(per, E, ranks)
+    return per
+
+
+def time_cpu(name, ranks, budget_s=12.0, max_passes=3, T=None):
+    from oracle import cpu_oracle
+    from moe_rd import workloads
+    cpu_oracle.lib()
+    cores = cpu_oracle.max_threads()
+    tensors, kw = [], None
+    for r in range(ranks):
+        t, kw = workloads.make(name, rank=r, T=T)
+        tensors.append(t)
+    E = tensors[0]["w"].shape[1]
+    Tn = tensors[0]["x"].shape[0]
+    times = []
+    t_start = time.perf_counter()
+    while len(times) < max_passes and (not times or time.perf_counter() - t_start < budget_s):
+        t0 = time.perf_counter()
+        cpu_pass(tensors, kw, ranks, E)
+        times.append(time.perf_counter() - t0)
+    best = statistics.median(times)
+    return {"value": ranks * Tn / best, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": f"{len(times)} full passes of {name} ({ranks} x {Tn} tokens), median",
+            "seconds_per_pass": best}
+
+
+def run_reference(args, rank, world):
+    if rank != 0:
+        return
+    name = args.workload
+    from moe_rd import workloads
+    spec = workloads.SPECS[name]
+    from oracle import cpu_oracle
+    cpu_oracle.lib()
+    tensors, kw = [], None
+    for r in range(world):
+        t, kw = workloads.make(name, rank=r)
+        tensors.append(t)
+    E, T = spec["E"], spec["T"]
+    t0 = time.perf_counter()
+    cpu_pass(tensors, kw, world, E)  # warm-up pass, also sizes the sample
+    first = time.perf_counter() - t0
+    budget = 180.0
+    if first * args.steps > budget:  # bounded sample: the leading tokens of every rank
+        T = max(128, int(T * budget / (first * args.steps)) // 128 * 128)
+        for t in tensors:
+            t["x"] = t["x"][:T].contiguous()
+        if "capacity" in kw and kw["capacity"]:
+            kw = dict(kw, capacity=int(-(-1.25 * T * spec["K"] // E)))
+    times = []
+    for _ in range(args.steps):
+        t0 = time.perf_counter()
+        cpu_pass(tensors, kw, world, E)
+        times.append(time.perf_counter() - t0)
+    total = sum(times)
+    value = world * T * len(times) / total
+    cores = cpu_oracle.max_threads()
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "config": workload_config(name, spec, world),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{len(times)} full passes of {name} ({world} x {T} tokens) on {cores} threads"},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference project has no CPU implementation of this path; this is the CPU oracle "
+                "(a port of the algorithm read from its CUDA source), OpenMP over all host threads",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(name, spec, world):
+    return {"workload": name, "tokens_per_rank": spec["T"], "hidden": spec["H"], "experts": spec["E"],
+            "top_k": spec["K"], "experts_per_rank": spec["E"] // world if name == "c5" else spec["E"],
+            "parallelism": f"ep{world}" if world > 1 else "single",
+            "l2": "flushed by a 256 MiB device write between steps"}
+
+
+def run_ours(args, rank, world, local_rank):
+    import torch
+    import torch.distributed as dist
+    import moe_rd
+    from moe_rd import workloads, _cabi
+    from moe_rd.runtime import Session
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the routing/dispatch path has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    name = args.workload
+    spec = workloads.SPECS[name]
+    tensors, kw = workloads.make(name, rank=rank)
+    T, H, E, K = spec["T"], spec["H"], spec["E"], spec["K"]
+    x = tensors["x"].to(dev)
+    w = tensors["w"].to(dev)
+    bias = None if tensors["bias"] is None else tensors["bias"].to(dev)
+    sess = Session(T, H, E, K, device=dev, w_dtype=w.dtype, **session_kwargs(kw))
+    ep = None
+    if world > 1:
+        from moe_rd.ep import ExpertParallel
+        ep = ExpertParallel(sess, dist.group.WORLD)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def step():
+        sess.run(x, w, bias)
+        if ep is not None:
+            ep.exchange()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        flush.zero_()
+        step()
+    barrier()
+    sess.status()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    launches0 = _cabi.launch_count()
+    barrier()
+    for s, e in ev:
+        flush.zero_()
+        s.record()
+        step()
+        e.record()
+    barrier()
+    launches = _cabi.launch_count() - launches0
+    times = [s.elapsed_time(e) for s, e in ev]
+    total_ms = torch.tensor([sum(times)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(total_ms, op=dist.ReduceOp.MAX)
+    total_ms = float(total_ms.item())
+    value = world * T * args.steps / (total_ms / 1e3)
+
+    # --- per-stage device times for the roofline of the dominant kernel (row scatter)
+    stage = []
+    for _ in range(min(args.steps, 10)):
+        flush.zero_()
+        stage.append(sess.run_timed(x, w, bias))
+    clocks = sampler.stop() if rank == 0 else None
+    stage_ms = [statistics.mean(s[i] for s in stage) for i in range(4)]
+    kept = int(sess.offsets[-1].item())
+    fp8 = kw.get("rows_format", "bf16") == "fp8"
+    row_bytes = H * (1 if fp8 else 2) + ((H // 128) * 4 if fp8 else 0)
+    scatter_bytes = T * H * 2 + kept * row_bytes + T * K * 4
+    op_bytes = workloads.algorithmic_bytes(T, H, E, K, w_bytes=w.element_size(), fp8=fp8, kept_rows=kept)
+    peak, peak_kind = measured_hbm_peak()
+    scatter_gbs = scatter_bytes / (stage_ms[3] * 1e-3) / 1e9
+    op_ms = total_ms / args.steps
+    roofline = {
+        "bound": "hbm", "kernel": "scatter_kernel", "achieved": scatter_gbs, "peak": peak, "unit": "GB/s",
+        "frac": scatter_gbs / peak, "peak_kind": f"{peak_kind} HBM copy bandwidth", "traffic": None,
+        "bytes_per_launch": scatter_bytes, "kernel_ms": stage_ms[3],
+        "stage_ms": {"gate": stage_ms[0], "route": stage_ms[1], "scan": stage_ms[2], "scatter": stage_ms[3]},
+        "whole_op": {"algorithmic_bytes": op_bytes, "ms": op_ms, "achieved": op_bytes / (op_ms * 1e-3) / 1e9,
+                     "frac_of_measured": op_bytes / (op_ms * 1e-3) / 1e9 / peak,
+                     "frac_of_8000": op_bytes / (op_ms * 1e-3) / 1e9 / 8000.0},
+    }
+
+    # --- end to end through the public callable with host buffers
+    x_host = tensors["x"].pin_memory()
+    res0 = moe_rd.route_dispatch(x, w, bias, **kw)
+    outs = [t for t in (res0.permuted, res0.scales, res0.offsets, res0.inverse_perm, res0.combine_weights) if t is not None]
+    host_out = [torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outs]
+    h2d = x_host.numel() * x_host.element_size()
+    d2h = sum(t.numel() * t.element_size() for t in outs)
+    del res0
+    e2e_steps = max(3, min(args.steps, 10))
+    ev2 = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(e2e_steps)]
+    x_in = torch.empty_like(x)
+
+    def e2e_step():
+        x_in.copy_(x_host, non_blocking=True)
+        r = moe_rd.route_dispatch(x_in, w, bias, **kw)
+        if ep is not None:
+            ep.exchange(r)
+        src = [t for t in (r.permuted, r.scales, r.offsets, r.inverse_perm, r.combine_weights) if t is not None]
+        for h, d in zip(host_out, src):
+            h.copy_(d, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    for s, e in ev2:
+        flush.zero_()
+        s.record()
+        e2e_step()
+        e.record()
+    barrier()
+    e2e_ms = torch.tensor([sum(s.elapsed_time(e) for s, e in ev2)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
+    e2e_value = world * T * e2e_steps / (float(e2e_ms.item()) / 1e3)
+
+    line = None
+    if rank == 0:
+        cpu = time_cpu(name, 1) if world == 1 else None
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": op_ms, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": workload_config(name, spec, world),
+            "roofline": roofline,
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps},
+            "gpu_launches": int(launches),
+            "clocks": clocks,
+            "kept_rows": kept,
+        }
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+    if line is not None:
+        print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
+    args = ap.parse_args()
+    rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
+    if world == 1 and args.gpus > 1:
+        raise SystemExit("launch with torchrun for --gpus > 1 (one process per GPU)")
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+    else:
+        run_ours(args, rank, world, local_rank)
+
+
+if __name__ == "__main__":
+    main()

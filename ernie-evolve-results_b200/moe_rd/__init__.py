@@ -1,0 +1,187 @@
+"""moe_rd — MoE sparse routing and dispatch on B200 (sm_100a).
+
+Host-side mirror of the operator boundary of the reference's
+``sol-execbench/029_moe_sparse_routing_and_dispatch`` (``kernel.cu::run``,
+kernel.cu:4067-4077): a Python callable that takes hidden states, the router
+(gate) weight and a bias, and returns expert-major permuted token rows,
+per-expert offsets, the inverse permutation and the combine weights.  It is
+registered as the torch custom op ``torch.ops.moe_rd.route_dispatch`` (CUDA
+only) on top of the C ABI in ``include/moe_rd.h``.  There is no CPU fallback
+and no alternative backend: without ``libmoe_rd.so`` or without a CUDA device
+every call raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from typing import NamedTuple, Optional
+
+import torch
+
+from . import _cabi
+from ._cabi import MoeRdError  # noqa: F401
+
+__all__ = ["route_dispatch", "RouteDispatchResult", "MoeRdError", "capacity_from_factor"]
+
+
+class RouteDispatchResult(NamedTuple):
+    permuted: torch.Tensor                # [T*K, H] bf16, or uint8 viewable as float8_e4m3fn
+    offsets: torch.Tensor                 # [E+1] int32, offsets[E] = kept pairs
+    inverse_perm: torch.Tensor            # [T, K] int32, -1 = dropped
+    combine_weights: torch.Tensor         # [T, K] fp32
+    scales: Optional[torch.Tensor]        # [T*K, H/128] fp32 (fp8 rows only)
+    drop_mask: torch.Tensor               # [T, K] uint8
+    expert_ids: torch.Tensor              # [T, K] int32
+    router_logits: Optional[torch.Tensor]  # [T, E] fp32 when requested
+    counts: torch.Tensor                  # [E] int32 pairs per expert before dropping
+
+
+def capacity_from_factor(factor: float, T: int, K: int, E: int) -> int:
+    """Rows kept per expert: ceil(factor * T * K / E)."""
+    return int(math.ceil(factor * T * K / E))
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+_BIAS_MODES = ("none", "logit", "select", "select_and_weight")
+
+
+def _impl(x, gate_weight, logit_bias, select_bias, given_logits, top_k, score_fn, n_groups,
+          topk_groups, group_topk, weight_from_key, renorm, routed_scale, norm_min, capacity,
+          rows_format, w_layout, gate_impl, scatter_impl, return_logits):
+    """CUDA implementation of ``moe_rd::route_dispatch`` (enqueue only, no host sync)."""
+    if not x.is_cuda:
+        raise RuntimeError("moe_rd.route_dispatch has no CPU path: hidden_states must be a CUDA tensor")
+    if x.dtype != torch.bfloat16:
+        raise TypeError("hidden_states must be bfloat16")
+    x2 = x.reshape(-1, x.shape[-1]).contiguous()
+    T, H = x2.shape
+    dev = x2.device
+    external = given_logits is not None
+    if external:
+        E = given_logits.shape[-1]
+        given_logits = given_logits.to(torch.float32).contiguous()
+        w = None
+        w_dtype = _cabi.W_DTYPE["bf16"]
+    else:
+        w = gate_weight.contiguous()
+        if w.dtype == torch.float32:
+            w_dtype = _cabi.W_DTYPE["fp32"]
+        elif w.dtype == torch.bfloat16:
+            w_dtype = _cabi.W_DTYPE["bf16"]
+        else:
+            raise TypeError("gate_weight must be float32 or bfloat16")
+        if w.dim() != 2:
+            raise ValueError("gate_weight must be 2-D")
+        wh, we = (w.shape[0], w.shape[1]) if w_layout == 0 else (w.shape[1], w.shape[0])
+        if wh != H:
+            raise ValueError(f"gate_weight does not match hidden size {H}")
+        E = we
+    K = int(top_k)
+    for b in (logit_bias, select_bias):
+        if b is not None and (b.dtype != torch.float32 or b.numel() != E or not b.is_cuda):
+            raise ValueError("bias must be a CUDA float32 tensor of E elements")
+
+    out_rows = T * K
+    if capacity > 0:
+        out_rows = min(out_rows, E * capacity)
+    fp8 = rows_format == _cabi.ROWS_FORMAT["fp8"]
+    with torch.cuda.device(dev):
+        permuted = torch.empty((out_rows, H), dtype=torch.uint8 if fp8 else torch.bfloat16, device=dev)
+        scales = torch.empty((out_rows, H // 128), dtype=torch.float32, device=dev) if fp8 else None
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        inv = torch.empty((T, K), dtype=torch.int32, device=dev)
+        weights = torch.empty((T, K), dtype=torch.float32, device=dev)
+        ids = torch.empty((T, K), dtype=torch.int32, device=dev)
+        drop = torch.empty((T, K), dtype=torch.uint8, device=dev)
+        counts = torch.empty(E, dtype=torch.int32, device=dev)
+        if external:
+            logits = given_logits
+        elif return_logits:
+            logits = torch.empty((T, E), dtype=torch.float32, device=dev)
+        else:
+            logits = None
+
+        p = _cabi.Params(
+            T=T, H=H, E=E, K=K, n_groups=n_groups, topk_groups=topk_groups, group_topk=group_topk,
+            score_fn=score_fn, weight_from_key=int(weight_from_key), renorm=int(renorm),
+            routed_scale=routed_scale, norm_min=norm_min, capacity=capacity, out_rows=out_rows,
+            rows_format=rows_format, w_dtype=w_dtype, w_layout=w_layout,
+            gate_impl=_cabi.GATE_IMPL["external"] if external else gate_impl,
+            scatter_impl=scatter_impl, reserved=0)
+        ws_bytes = _cabi.workspace_bytes(p)
+        ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+        bufs = _cabi.Buffers(
+            x=_ptr(x2), gate_w=_ptr(w), logit_bias=_ptr(logit_bias), select_bias=_ptr(select_bias),
+            permuted=_ptr(permuted), scales=_ptr(scales), offsets=_ptr(offsets), inverse_perm=_ptr(inv),
+            combine_weights=_ptr(weights), expert_ids=_ptr(ids), drop_mask=_ptr(drop),
+            router_logits=_ptr(logits), counts=_ptr(counts))
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+        _cabi.check(_cabi.lib().moe_rd_route_dispatch(
+            ctypes.byref(p), ctypes.byref(bufs), ctypes.c_void_p(ws.data_ptr()), ws_bytes, stream))
+        # ws goes back to the caching allocator here; reuse is ordered on this stream
+    empty = torch.empty(0, device=dev)
+    return [permuted, offsets, inv, weights, scales if scales is not None else empty, drop, ids,
+            logits if (logits is not None and not external) else empty, counts]
+
+
+_SCHEMA = ("route_dispatch(Tensor hidden_states, Tensor? gate_weight, Tensor? logit_bias, "
+           "Tensor? select_bias, Tensor? given_logits, int top_k, int score_fn, int n_groups, "
+           "int topk_groups, int group_topk, bool weight_from_key, bool renorm, float routed_scale, "
+           "float norm_min, int capacity, int rows_format, int w_layout, int gate_impl, "
+           "int scatter_impl, bool return_logits) -> Tensor[]")
+
+_torch_lib = torch.library.Library("moe_rd", "DEF")
+_torch_lib.define(_SCHEMA)
+_torch_lib.impl("route_dispatch", _impl, "CUDA")
+
+
+def route_dispatch(hidden_states: torch.Tensor, gate_weight: Optional[torch.Tensor],
+                   bias: Optional[torch.Tensor] = None, *, top_k: int,
+                   score_fn: str = "softmax", bias_mode: str = "select",
+                   n_groups: int = 1, topk_groups: int = 1, group_topk: int = 1,
+                   renorm: bool = True, routed_scale: float = 1.0, norm_min: float = 1e-20,
+                   capacity_factor: Optional[float] = None, capacity: Optional[int] = None,
+                   rows_format: str = "bf16", w_layout: str = "HE", gate_impl: str = "auto",
+                   scatter_impl: str = "auto", return_logits: bool = False,
+                   given_logits: Optional[torch.Tensor] = None) -> RouteDispatchResult:
+    """Route tokens to experts and build the expert-major dispatch buffers.
+
+    hidden_states: [..., H] bf16 (CUDA).  gate_weight: [H, E] (``w_layout="HE"``)
+    or [E, H] (``"EH"``, the reference's layout, kernel.cu:4324), fp32 or bf16.
+    bias: [E] fp32, used according to ``bias_mode``:
+      "logit"             added to the logits before scoring;
+      "select"            added to the scores for selection only;
+      "select_and_weight" added to the scores for selection and kept in the
+                          combine weights, the reference's behaviour
+                          (kernel.cu:1865-1866, 1891, 1909).
+    capacity / capacity_factor: rows kept per expert; later pairs (token order)
+    are dropped.  rows_format "fp8" quantises rows to e4m3 with one fp32 scale
+    per 128 elements.  ``given_logits`` skips the gate product.
+    """
+    if bias_mode not in _BIAS_MODES:
+        raise ValueError(f"bias_mode must be one of {_BIAS_MODES}")
+    logit_bias = bias if (bias is not None and bias_mode == "logit") else None
+    select_bias = bias if (bias is not None and bias_mode in ("select", "select_and_weight")) else None
+    T = hidden_states.numel() // hidden_states.shape[-1]
+    if given_logits is not None:
+        E = given_logits.shape[-1]
+    else:
+        E = gate_weight.shape[1] if w_layout == "HE" else gate_weight.shape[0]
+    if capacity is None:
+        capacity = capacity_from_factor(capacity_factor, T, top_k, E) if capacity_factor else 0
+    out = torch.ops.moe_rd.route_dispatch(
+        hidden_states, gate_weight, logit_bias, select_bias, given_logits, top_k,
+        _cabi.SCORE_FN[score_fn], n_groups, topk_groups, group_topk,
+        bias_mode == "select_and_weight", renorm, float(routed_scale), float(norm_min),
+        int(capacity), _cabi.ROWS_FORMAT[rows_format], _cabi.W_LAYOUT[w_layout],
+        _cabi.GATE_IMPL[gate_impl], _cabi.SCATTER_IMPL[scatter_impl], return_logits)
+    permuted, offsets, inv, weights, scales, drop, ids, logits, counts = out
+    if given_logits is not None:
+        logits = given_logits
+    elif not return_logits:
+        logits = None
+    return RouteDispatchResult(permuted, offsets, inv, weights,
+                               scales if rows_format == "fp8" else None, drop, ids, logits, counts)

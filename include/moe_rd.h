@@ -1,0 +1,149 @@
+/*
+ * moe_rd — MoE sparse routing and dispatch for NVIDIA B200 (sm_100a).
+ *
+ * C ABI of libmoe_rd.so.  Plain pointers and sizes only; every pointer in
+ * moe_rd_buffers is DEVICE memory owned by the caller, and the library never
+ * allocates or frees on a call path (destination passing).  All work is
+ * enqueued on the caller's stream; no entry point synchronises the host
+ * unless its comment says so.  Functions return 0 or a negative MOE_RD_E_*.
+ *
+ * "Reference" below is ernie-research/ERNIE-Evolve-Results; citations are
+ * relative to sol-execbench/029_moe_sparse_routing_and_dispatch/.
+ */
+#ifndef MOE_RD_H_
+#define MOE_RD_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOE_RD_VERSION 1
+
+/* error codes */
+#define MOE_RD_OK 0
+#define MOE_RD_E_NULL (-1)        /* a required pointer is NULL */
+#define MOE_RD_E_SHAPE (-2)       /* T/H/E/K outside the supported range */
+#define MOE_RD_E_GROUPS (-3)      /* group-limited routing parameters inconsistent */
+#define MOE_RD_E_ALIGN (-4)       /* pointer or row pitch not 16-byte aligned */
+#define MOE_RD_E_WORKSPACE (-5)   /* workspace too small or misaligned */
+#define MOE_RD_E_ENUM (-6)        /* unknown enum value */
+#define MOE_RD_E_CUDA (-7)        /* a CUDA call failed; see moe_rd_last_cuda_error */
+#define MOE_RD_E_UNSUPPORTED (-8) /* combination not implemented */
+#define MOE_RD_E_DEVICE (-9)      /* device-side check failed; see moe_rd_read_status */
+#define MOE_RD_E_TOO_LARGE (-10)  /* problem exceeds a fixed-size resource */
+
+/* enums (int32 fields of moe_rd_params) */
+enum { MOE_RD_SCORE_SOFTMAX = 0, MOE_RD_SCORE_SIGMOID = 1 };
+enum { MOE_RD_W_F32 = 0, MOE_RD_W_BF16 = 1 };
+enum { MOE_RD_W_LAYOUT_HE = 0 /* [H,E] row-major */, MOE_RD_W_LAYOUT_EH = 1 /* [E,H] */ };
+enum { MOE_RD_ROWS_BF16 = 0, MOE_RD_ROWS_FP8_E4M3_B128 = 1 };
+enum {
+  MOE_RD_GATE_AUTO = 0,     /* E < 64: warp GEMV; E >= 64 with bf16 weights: tcgen05 */
+  MOE_RD_GATE_SIMT = 1,     /* fixed-order fp32 FMA product, any E */
+  MOE_RD_GATE_UMMA = 2,     /* tcgen05/TMEM tiles fed by TMA (bf16 weights, E % 16 == 0, E <= 256) */
+  MOE_RD_GATE_EXTERNAL = 3  /* logits supplied by the caller in router_logits */
+};
+enum { MOE_RD_SCATTER_AUTO = 0, MOE_RD_SCATTER_SIMT = 1, MOE_RD_SCATTER_BULK = 2 };
+
+/*
+ * Problem description.  Replaces the compile-time constants NE/TOPK and the
+ * scalar arguments of the reference's run() (kernel.cu:1582-1583, 4067-4077).
+ */
+typedef struct moe_rd_params {
+  int64_t T;            /* tokens (rows of x) */
+  int32_t H;            /* hidden size; H % 8 == 0, and H % 128 == 0 for fp8 rows */
+  int32_t E;            /* experts, 1..256 */
+  int32_t K;            /* experts per token, 1..32, K <= E */
+  int32_t n_groups;     /* 1 = no group limit; else E % n_groups == 0, n_groups <= 32 */
+  int32_t topk_groups;  /* groups kept per token */
+  int32_t group_topk;   /* a group's score = sum of its group_topk largest keys */
+  int32_t score_fn;     /* MOE_RD_SCORE_* */
+  int32_t weight_from_key; /* 1: weights from score+select_bias as the reference does
+                              (kernel.cu:1891,1909); 0: from the unbiased score */
+  int32_t renorm;       /* 1: w = u / max(sum u, norm_min) */
+  float routed_scale;   /* weights are multiplied by this last */
+  float norm_min;       /* the reference's norm_min (kernel.cu:1909) */
+  int64_t capacity;     /* rows kept per expert, 0 = unlimited; pairs beyond it are
+                           dropped in token order */
+  int64_t out_rows;     /* rows the caller allocated in permuted/scales (>= kept pairs;
+                           T*K always suffices) */
+  int32_t rows_format;  /* MOE_RD_ROWS_* */
+  int32_t w_dtype;      /* MOE_RD_W_* */
+  int32_t w_layout;     /* MOE_RD_W_LAYOUT_* */
+  int32_t gate_impl;    /* MOE_RD_GATE_* */
+  int32_t scatter_impl; /* MOE_RD_SCATTER_* */
+  int32_t reserved;
+} moe_rd_params;
+
+/*
+ * Device buffers.  The data contract between routing and expert compute that
+ * the reference keeps in its arena (kernel.cu:4208-4222, 4304-4306): sel,
+ * wsel, offs/cursor, inv, xg, router_logits.
+ */
+typedef struct moe_rd_buffers {
+  const void* x;             /* [T,H] bf16 row-major, 16-byte aligned */
+  const void* gate_w;        /* [H,E] or [E,H], fp32 or bf16 */
+  const float* logit_bias;   /* [E] added to the logits before scoring, or NULL */
+  const float* select_bias;  /* [E] added to the scores to form selection keys, or NULL
+                                (the reference's e_score_correction_bias) */
+  void* permuted;            /* [out_rows,H] bf16, or [out_rows,H] fp8-e4m3 bytes */
+  float* scales;             /* [out_rows,H/128] fp32 (fp8 rows only) */
+  int32_t* offsets;          /* [E+1] first row of each expert, offsets[E] = kept pairs */
+  int32_t* inverse_perm;     /* [T,K] row of pair (t,k) in permuted, -1 if dropped */
+  float* combine_weights;    /* [T,K] */
+  int32_t* expert_ids;       /* [T,K] slot k = k-th pick, or NULL */
+  uint8_t* drop_mask;        /* [T,K] 1 = dropped by the capacity limit, or NULL */
+  float* router_logits;      /* [T,E] fp32: optional output; INPUT for MOE_RD_GATE_EXTERNAL */
+  int32_t* counts;           /* [E] pairs routed to each expert before dropping, or NULL */
+} moe_rd_buffers;
+
+/* Bytes of scratch moe_rd_route_dispatch needs for these parameters. */
+int moe_rd_workspace_bytes(const moe_rd_params* p, size_t* bytes);
+
+/*
+ * Router -> top-k -> offsets -> dispatch -> row scatter, steps 1-6 of the
+ * reference's run() (kernel.cu:4323-4430: wsplit_kernel, the router GEMM,
+ * topk_kernel, offsets_kernel, dispatch_kernel, gather_kernel), enqueued on
+ * `stream` (a cudaStream_t) with no host synchronisation.  `workspace` is
+ * device memory, 256-byte aligned, of at least moe_rd_workspace_bytes bytes.
+ */
+int moe_rd_route_dispatch(const moe_rd_params* p, const moe_rd_buffers* b,
+                          void* workspace, size_t workspace_bytes, void* stream);
+
+/*
+ * Same work as moe_rd_route_dispatch, but with a CUDA event recorded on
+ * `stream` between the stages; synchronises the stream and returns the device
+ * time of each stage in milliseconds: stage_ms[0] gate product, [1] scoring /
+ * top-k / tile histogram, [2] scans, [3] row scatter.  For measurement only
+ * (the reference's per-kernel figures come from an external profiler,
+ * kernel.cu:865-890); it creates and destroys events, so keep it off hot paths.
+ */
+int moe_rd_route_dispatch_timed(const moe_rd_params* p, const moe_rd_buffers* b,
+                                void* workspace, size_t workspace_bytes, void* stream,
+                                float stage_ms[4]);
+
+/*
+ * Copies the 8-word device status block of the last call that used
+ * `workspace` to the host (synchronises `stream`).  status[0] != 0 means a
+ * device-side bound check failed (the offending access was skipped);
+ * status[1..3] hold the check id and the bad values.  Returns
+ * MOE_RD_E_DEVICE in that case.  The reference has no counterpart: it relies
+ * on external compute-sanitizer runs (kernel.cu:4193-4195).
+ */
+int moe_rd_read_status(const void* workspace, void* stream, int32_t status[8]);
+
+/* Kernels this library launched since it was loaded (all threads). */
+int64_t moe_rd_launch_count(void);
+
+const char* moe_rd_strerror(int code);
+/* cudaError_t of the last failed CUDA call on this thread, as text. */
+const char* moe_rd_last_cuda_error(void);
+int moe_rd_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOE_RD_H_ */
