@@ -253,6 +253,13 @@ def run_ours(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+        # nvidia-smi needs a moment to start and samples every 100 ms: keep the same
+        # load running (untimed) until it has had time to see clocks under load.
+        t_hold = time.perf_counter()
+        while time.perf_counter() - t_hold < 1.5:
+            for _ in range(20):
+                step()
+            torch.cuda.synchronize()
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     launches0 = _cabi.launch_count()
     barrier()

@@ -17,6 +17,7 @@ void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 cudaError_t init_route_attributes();
 cudaError_t init_umma_attributes();
+cudaError_t init_gemv_attributes();
 
 static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -28,9 +29,14 @@ static bool umma_eligible(const moe_rd_params& p) {
 int make_plan(const moe_rd_params& p, Plan* plan) {
   plan->ntiles = (int)((p.T + kTile - 1) / kTile);
   int gate = p.gate_impl;
-  if (gate == MOE_RD_GATE_AUTO)
-    gate = (p.E >= 64 && umma_eligible(p)) ? MOE_RD_GATE_UMMA : MOE_RD_GATE_SIMT;
+  if (gate == MOE_RD_GATE_AUTO) {
+    if (gemv_eligible(p))
+      gate = MOE_RD_GATE_GEMV;
+    else
+      gate = (p.E >= 64 && umma_eligible(p)) ? MOE_RD_GATE_UMMA : MOE_RD_GATE_SIMT;
+  }
   if (gate == MOE_RD_GATE_UMMA && !umma_eligible(p)) return MOE_RD_E_UNSUPPORTED;
+  if (gate == MOE_RD_GATE_GEMV && !gemv_eligible(p)) return MOE_RD_E_UNSUPPORTED;
   plan->gate = gate;
   plan->scatter = p.scatter_impl == MOE_RD_SCATTER_AUTO ? MOE_RD_SCATTER_SIMT : p.scatter_impl;
   // Split K so that about two CTAs per SM are in flight (148 SMs).
@@ -82,7 +88,7 @@ static int validate(const moe_rd_params* p) {
   if (p->w_layout != MOE_RD_W_LAYOUT_HE && p->w_layout != MOE_RD_W_LAYOUT_EH) return MOE_RD_E_ENUM;
   if (p->rows_format != MOE_RD_ROWS_BF16 && p->rows_format != MOE_RD_ROWS_FP8_E4M3_B128)
     return MOE_RD_E_ENUM;
-  if (p->gate_impl < MOE_RD_GATE_AUTO || p->gate_impl > MOE_RD_GATE_EXTERNAL) return MOE_RD_E_ENUM;
+  if (p->gate_impl < MOE_RD_GATE_AUTO || p->gate_impl > MOE_RD_GATE_GEMV) return MOE_RD_E_ENUM;
   if (p->scatter_impl < MOE_RD_SCATTER_AUTO || p->scatter_impl > MOE_RD_SCATTER_BULK)
     return MOE_RD_E_ENUM;
   if (p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128 && p->H % 128 != 0) return MOE_RD_E_SHAPE;
@@ -109,6 +115,8 @@ static cudaError_t init_device_once() {
   e = init_route_attributes();
   if (e != cudaSuccess) return e;
   e = init_umma_attributes();
+  if (e != cudaSuccess) return e;
+  e = init_gemv_attributes();
   if (e != cudaSuccess) return e;
   done[dev] = true;
   return cudaSuccess;
@@ -175,9 +183,10 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   rc = make_plan(*p, &plan);
   if (rc != MOE_RD_OK) return rc;
   if (plan.scatter == MOE_RD_SCATTER_BULK) return MOE_RD_E_UNSUPPORTED;
-  if (b->offsets == nullptr || b->inverse_perm == nullptr || b->combine_weights == nullptr)
+  if (b->offsets == nullptr) return MOE_RD_E_NULL;
+  if (p->T > 0 && (b->x == nullptr || b->permuted == nullptr || b->inverse_perm == nullptr ||
+                   b->combine_weights == nullptr))
     return MOE_RD_E_NULL;
-  if (p->T > 0 && (b->x == nullptr || b->permuted == nullptr)) return MOE_RD_E_NULL;
   if (plan.gate == MOE_RD_GATE_EXTERNAL ? (p->T > 0 && b->router_logits == nullptr)
                                         : (p->T > 0 && b->gate_w == nullptr))
     return MOE_RD_E_NULL;
@@ -191,7 +200,9 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   if (p->out_rows < p->T * p->K && (p->capacity == 0 || p->out_rows < (int64_t)p->E * p->capacity))
     return MOE_RD_E_SHAPE;
 
-  const bool need_logits = plan.gate != MOE_RD_GATE_EXTERNAL && b->router_logits == nullptr;
+  // The fused GEMV keeps logits in shared memory; it writes them out only on request.
+  const bool need_logits = plan.gate != MOE_RD_GATE_EXTERNAL && plan.gate != MOE_RD_GATE_GEMV &&
+                           b->router_logits == nullptr;
   const bool need_ids = b->expert_ids == nullptr;
   Workspace w;
   carve(*p, plan, need_logits, need_ids, &w);
@@ -219,8 +230,12 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
     }
   }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[1], s));
-  if (p->T > 0)
-    MOE_RD_CUDA(launch_route(*p, *b, plan, logits, ids, pair_rank, tile_base, ticket, status, s));
+  if (p->T > 0) {
+    if (plan.gate == MOE_RD_GATE_GEMV)
+      MOE_RD_CUDA(launch_gemv_route(*p, *b, plan, b->router_logits, ids, pair_rank, tile_base, s));
+    else
+      MOE_RD_CUDA(launch_route(*p, *b, plan, logits, ids, pair_rank, tile_base, ticket, status, s));
+  }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[2], s));
   MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, ticket, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[3], s));

@@ -1,0 +1,247 @@
+// Device code shared by the routing kernels: per-token scoring / top-K, and
+// the deterministic per-tile histogram with in-tile stable ranks.
+//
+// Follows topk_kernel of the reference (kernel.cu:1829-1920): one warp per
+// token, experts strided over lanes (expert e lives in lane e%32, register
+// e/32), softmax as max / exp / sum / reciprocal-multiply (1857-1866), bias
+// added to the score to form the selection key (1865-1866), K rounds of warp
+// arg-max with lowest-index tie-break (1872-1901), weights u / max(sum u,
+// norm_min) (1909).  Added: sigmoid scoring, selection-only bias,
+// group-limited selection, a final scale.  The reference's 5-step shuffle
+// arg-max is replaced by two redux.sync operations on order-preserving integer
+// images of the keys (max of the keys, then min of the indices that hold it),
+// which selects the same expert.
+//
+// The reference ranks a pair inside its expert with shared and global atomics
+// (dispatch_body, kernel.cu:2155-2158), so its slot order depends on
+// scheduling.  Here a block owns a tile of kTile consecutive tokens, counts
+// every 32 consecutive pairs with __match_any_sync and prefix-sums the counts
+// in pair order: a pair's rank is a pure function of the ids.
+#pragma once
+
+#include "common.cuh"
+
+namespace moe_rd {
+
+struct RouteArgs {
+  const float* logits;       // [T,E] (unused by the fused gate kernel)
+  const float* select_bias;  // [E] or null
+  int32_t* ids;              // [T,K]
+  float* weights;            // [T,K]
+  int32_t* pair_rank;        // [T*K]
+  int32_t* tile_counts;      // [E][ntiles]
+  int64_t T;
+  int E, K, ntiles;
+  int n_groups, topk_groups, group_topk;
+  int score_fn, weight_from_key, renorm;
+  float routed_scale, norm_min;
+};
+
+// Order-preserving map fp32 -> uint32 (-0.0 is folded onto +0.0 so that keys
+// that compare equal as floats have equal images).
+__device__ __forceinline__ uint32_t ord_key(float f) {
+  uint32_t u = __float_as_uint(f);
+  if (u == 0x80000000u) u = 0u;
+  return u ^ ((uint32_t)((int32_t)u >> 31) | 0x80000000u);
+}
+__device__ __forceinline__ float ord_value(uint32_t k) {
+  return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
+
+// Scores one token held as z[i] = logit of expert lane + 32*i and selects its
+// K experts.  On return lane k < K holds slot k: `mysel` the expert, `myw` the
+// combine weight.  All 32 lanes of the warp must call.
+template <int EPL>
+__device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)[EPL], int lane,
+                                            int& mysel, float& myw) {
+  float sc[EPL];
+  uint32_t ok[EPL];  // ordered images of the selection keys; 0 = not eligible
+  if (a.score_fn == MOE_RD_SCORE_SOFTMAX) {
+    uint32_t mk = 0u;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i)
+      if (lane + 32 * i < a.E) mk = max(mk, ord_key(z[i]));
+    const float m = ord_value(__reduce_max_sync(kFull, mk));
+    float part = 0.0f;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const float p = lane + 32 * i < a.E ? exp_ieee(__fsub_rn(z[i], m)) : 0.0f;
+      sc[i] = p;
+      part = __fadd_rn(part, p);
+    }
+    const float rs = __fdiv_rn(1.0f, warp_tree_sum(part));
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) sc[i] = __fmul_rn(sc[i], rs);
+  } else {
+#pragma unroll
+    for (int i = 0; i < EPL; ++i)
+      sc[i] = lane + 32 * i < a.E ? __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_ieee(-z[i]))) : 0.0f;
+  }
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int e = lane + 32 * i;
+    float key = sc[i];
+    if (e < a.E && a.select_bias != nullptr) key = __fadd_rn(key, __ldg(a.select_bias + e));
+    ok[i] = e < a.E ? ord_key(key) : 0u;
+  }
+
+  if (a.n_groups > 1) {
+    const int gs = a.E / a.n_groups;
+    float mygs = 0.0f;  // lane g keeps the score of group g
+    if ((gs & 31) == 0 && a.group_topk <= 2) {
+      // A group is a whole number of registers: m = gs/32 of them per lane.
+      const int m = gs >> 5;
+      for (int g = 0; g < a.n_groups; ++g) {
+        uint32_t l1 = 0u, l2 = 0u;  // the lane's two largest images inside the group
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+          if (i >= g * m && i < (g + 1) * m) {
+            const uint32_t v = ok[i];
+            if (v > l1) {
+              l2 = l1;
+              l1 = v;
+            } else if (v > l2) {
+              l2 = v;
+            }
+          }
+        }
+        const uint32_t m1 = __reduce_max_sync(kFull, l1);
+        float sum = ord_value(m1);
+        if (a.group_topk == 2) {
+          // Second largest = largest once ONE instance of m1 is removed.
+          const unsigned holders = __ballot_sync(kFull, l1 == m1);
+          uint32_t m2 = m1;
+          if (__popc(holders) < 2) m2 = __reduce_max_sync(kFull, l1 == m1 ? l2 : l1);
+          sum = __fadd_rn(sum, ord_value(m2));
+        }
+        if (lane == g) mygs = sum;
+      }
+    } else {
+      for (int g = 0; g < a.n_groups; ++g) {
+        const int lo = g * gs, hi = lo + gs;
+        unsigned gtaken = 0;
+        float sum = 0.0f;
+        for (int r = 0; r < a.group_topk; ++r) {
+          uint32_t bk = 0u;
+          int bi = 0x7fffffff;
+#pragma unroll
+          for (int i = 0; i < EPL; ++i) {
+            const int e = lane + 32 * i;
+            if (e >= lo && e < hi && !((gtaken >> i) & 1u) && ok[i] > bk) {
+              bk = ok[i];
+              bi = e;
+            }
+          }
+          const uint32_t mx = __reduce_max_sync(kFull, bk);
+          const int win = (int)__reduce_min_sync(kFull, (unsigned)(bk == mx ? bi : 0x7fffffff));
+          if (win < a.E && (win & 31) == lane) gtaken |= 1u << (win >> 5);
+          const float bv = ord_value(mx);
+          sum = r == 0 ? bv : __fadd_rn(sum, bv);
+        }
+        if (lane == g) mygs = sum;
+      }
+    }
+    int rank = 0;
+    for (int o = 0; o < a.n_groups; ++o) {
+      const float og = __shfl_sync(kFull, mygs, o);
+      if (og > mygs || (og == mygs && o < lane)) ++rank;
+    }
+    const unsigned keep = __ballot_sync(kFull, lane < a.n_groups && rank < a.topk_groups);
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      const int e = lane + 32 * i;
+      if (e < a.E && !((keep >> (e / gs)) & 1u)) ok[i] = 0u;
+    }
+  }
+
+  unsigned taken = 0;
+  float tot = 0.0f, myu = 0.0f;
+  mysel = 0;
+  for (int k = 0; k < a.K; ++k) {
+    uint32_t bk = 0u;
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) {
+      if (!((taken >> i) & 1u) && ok[i] > bk) {  // strict: the lowest register wins ties
+        bk = ok[i];
+        bi = lane + 32 * i;
+      }
+    }
+    const uint32_t mx = __reduce_max_sync(kFull, bk);
+    int win = (int)__reduce_min_sync(kFull, (unsigned)(bk == mx ? bi : 0x7fffffff));
+    win = min(max(win, 0), a.E - 1);  // only non-finite inputs can get here out of range
+    const int oi = win >> 5, ol = win & 31;
+    float cand = 0.0f;
+    if (a.weight_from_key) {
+      cand = ord_value(mx);
+    } else {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i)
+        if (i == oi) cand = sc[i];
+      cand = __shfl_sync(kFull, cand, ol);
+    }
+    if (ol == lane) taken |= 1u << oi;
+    tot = __fadd_rn(tot, cand);
+    if (lane == k) {
+      mysel = win;
+      myu = cand;
+    }
+  }
+  const float wv = a.renorm ? __fdiv_rn(myu, fmaxf(tot, a.norm_min)) : myu;
+  myw = __fmul_rn(wv, a.routed_scale);
+}
+
+// Shared memory a tile needs for ids + chunk counts.
+__host__ __device__ inline size_t tile_hist_smem(int K, int E) {
+  return (size_t)kTile * K * 4 + (size_t)((kTile * K + 31) / 32) * E * 2 + 16;
+}
+
+// In-tile stable ranks and per-expert tile counts from the ids in s_ids[0..P).
+// Called by every thread of the block after s_ids is complete (a barrier has
+// been passed); s_cc must hold ceil(P/32)*E uint16.  Ends with a barrier.
+template <int NTHREADS>
+__device__ __forceinline__ void tile_histogram(const RouteArgs& a, const int32_t* s_ids,
+                                               uint16_t* s_cc, int P, int tile, int64_t t0) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int nwarps = NTHREADS / 32;
+  const int nch = (P + 31) >> 5;
+  {
+    uint32_t* z32 = reinterpret_cast<uint32_t*>(s_cc);
+    const int nw = (nch * a.E + 1) >> 1;
+    for (int i = tid; i < nw; i += NTHREADS) z32[i] = 0u;
+  }
+  __syncthreads();
+  // Count every 32 consecutive pairs per expert.
+  for (int c = warp; c < nch; c += nwarps) {
+    const int p = c * 32 + lane;
+    const int e = p < P ? s_ids[p] : -1;
+    const unsigned m = __match_any_sync(kFull, e);
+    if (e >= 0 && (m & ((1u << lane) - 1u)) == 0u) s_cc[c * a.E + e] = (uint16_t)__popc(m);
+  }
+  __syncthreads();
+  // Exclusive prefix over the chunks of each expert, in pair order.
+  for (int e = tid; e < a.E; e += NTHREADS) {
+    int run = 0;
+    for (int c = 0; c < nch; ++c) {
+      const int v = s_cc[c * a.E + e];
+      s_cc[c * a.E + e] = (uint16_t)run;
+      run += v;
+    }
+    a.tile_counts[(size_t)e * a.ntiles + tile] = run;
+  }
+  __syncthreads();
+  for (int c = warp; c < nch; c += nwarps) {
+    const int p = c * 32 + lane;
+    const int e = p < P ? s_ids[p] : -1;
+    const unsigned m = __match_any_sync(kFull, e);
+    if (e >= 0)
+      a.pair_rank[(size_t)t0 * a.K + p] = (int)s_cc[c * a.E + e] + __popc(m & ((1u << lane) - 1u));
+  }
+  __syncthreads();
+}
+
+void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
+                     const float* logits, int32_t* ids, int32_t* pair_rank, int32_t* tile_base,
+                     RouteArgs* a);
+
+}  // namespace moe_rd

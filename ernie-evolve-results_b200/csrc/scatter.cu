@@ -10,7 +10,11 @@
 // A pair's destination is  offsets[e] + tile_base[e][tile] + rank_in_tile ,
 // all integers produced by the route and scan kernels, so the slot order is
 // the stable (token, slot) order.  Pairs whose rank inside the expert reaches
-// the capacity get inverse_perm = -1 and are not written.
+// the capacity get inverse_perm = -1 and are not written.  positions_kernel
+// turns those integers into inverse_perm / drop_mask; scatter_kernel is then a
+// pure streaming kernel whose work units (a 2 KB slice of a bf16 row, or 512
+// elements = four scale blocks of an fp8 row) are dealt to warps grid-stride,
+// so the load is even whatever T, H and K are.
 //
 // fp8 rows follow the reference's per-row int8 quantiser convention
 // (xquant_body, kernel.cu:2573-2591) applied per 128 elements with QMAX = 448:
@@ -23,21 +27,52 @@ namespace moe_rd {
 namespace {
 
 constexpr int kScatterThreads = 256;
-constexpr int kGroup = 8;  // tokens per block iteration = warps per block
+constexpr int kScatterWarps = kScatterThreads / 32;
 
-struct ScatterArgs {
-  const uint16_t* x;
+struct PositionArgs {
   const int32_t* ids;
   const int32_t* pair_rank;
   const int32_t* tile_base;  // [E][ntiles], scanned
   const int32_t* offsets;    // [E+1]
   int32_t* inverse_perm;
   uint8_t* drop_mask;
+  int32_t* status;
+  int64_t P, capacity, out_rows;
+  int E, K, ntiles;
+};
+
+__global__ void __launch_bounds__(256) positions_kernel(const PositionArgs a) {
+  const int64_t s = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  if (s >= a.P) return;
+  const int64_t t = s / a.K;
+  const int e = a.ids[s];
+  int pos = -1;
+  bool dropped = false;
+  if (e < 0 || e >= a.E) {
+    report(a.status, 1, e, (int)s);
+  } else {
+    const int64_t r =
+        (int64_t)a.tile_base[(size_t)e * a.ntiles + (int)(t / kTile)] + a.pair_rank[s];
+    dropped = a.capacity > 0 && r >= a.capacity;
+    if (!dropped) {
+      const int64_t q = (int64_t)a.offsets[e] + r;
+      if (q < 0 || q >= a.out_rows)
+        report(a.status, 2, (int)q, (int)s);
+      else
+        pos = (int)q;
+    }
+  }
+  a.inverse_perm[s] = pos;
+  if (a.drop_mask != nullptr) a.drop_mask[s] = dropped ? 1 : 0;
+}
+
+struct ScatterArgs {
+  const uint16_t* x;
+  const int32_t* inverse_perm;
   void* rows;
   float* scales;
-  int32_t* status;
-  int64_t T, capacity, out_rows;
-  int H, E, K, ntiles;
+  int64_t T;
+  int H, K;
 };
 
 __device__ __forceinline__ uint32_t abs_bf16x2(uint32_t v) { return v & 0x7fff7fffu; }
@@ -60,105 +95,111 @@ __device__ __forceinline__ uint32_t quant4(uint32_t a, uint32_t b, float inv) {
   return q0 | (q1 << 16);
 }
 
+// Work units are numbered u = t * upr + c (row t, slice c).  A warp walks
+// u = w, w + W, w + 2W, ...; (t, c) advance without a division.
+struct UnitWalk {
+  int64_t t;
+  int c, dq, dr, upr;
+  __device__ UnitWalk(int64_t first, int64_t stride, int units_per_row) {
+    upr = units_per_row;
+    t = first / upr;
+    c = (int)(first - t * upr);
+    dq = (int)(stride / upr);
+    dr = (int)(stride - (int64_t)dq * upr);
+  }
+  __device__ void next() {
+    t += dq;
+    c += dr;
+    if (c >= upr) {
+      c -= upr;
+      ++t;
+    }
+  }
+};
+
 template <int FMT>
 __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterArgs a) {
-  extern __shared__ int s_pos[];  // [kGroup*K]
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int64_t ngroups = (a.T + kGroup - 1) / kGroup;
+  const int lane = threadIdx.x & 31;
+  const int64_t w0 = (int64_t)blockIdx.x * kScatterWarps + (threadIdx.x >> 5);
+  const int64_t W = (int64_t)gridDim.x * kScatterWarps;
 
-  for (int64_t g = blockIdx.x; g < ngroups; g += gridDim.x) {
-    const int64_t t0 = g * kGroup;
-    const int ng = (int)min((int64_t)kGroup, a.T - t0);
-    __syncthreads();  // every warp is done reading s_pos of the previous group
-    for (int p = tid; p < ng * a.K; p += kScatterThreads) {
-      const size_t s = (size_t)t0 * a.K + p;
-      const int64_t t = t0 + p / a.K;
-      const int e = a.ids[s];
-      int pos = -1;
-      bool dropped = false;
-      if (e < 0 || e >= a.E) {
-        report(a.status, 1, e, (int)s);
-      } else {
-        const int64_t r =
-            (int64_t)a.tile_base[(size_t)e * a.ntiles + (int)(t / kTile)] + a.pair_rank[s];
-        dropped = a.capacity > 0 && r >= a.capacity;
-        if (!dropped) {
-          const int64_t q = (int64_t)a.offsets[e] + r;
-          if (q < 0 || q >= a.out_rows)
-            report(a.status, 2, (int)q, (int)s);
-          else
-            pos = (int)q;
-        }
+  if (FMT == MOE_RD_ROWS_BF16) {
+    // unit = 128 uint4 (2 KB) of a row: four 16-byte loads per lane
+    const int nvec = a.H >> 3;
+    const int upr = (nvec + 127) >> 7;
+    const uint4* x4 = reinterpret_cast<const uint4*>(a.x);
+    uint4* dst = reinterpret_cast<uint4*>(a.rows);
+    UnitWalk wk(w0, W, upr);
+    for (; wk.t < a.T; wk.next()) {
+      const uint4* src = x4 + (size_t)wk.t * nvec;
+      const int vb = wk.c * 128 + lane;
+      uint4 val[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (vb + 32 * u < nvec) val[u] = __ldg(src + vb + 32 * u);
+      const int32_t* pos = a.inverse_perm + (size_t)wk.t * a.K;
+      for (int k = 0; k < a.K; ++k) {
+        const int q = __ldg(pos + k);
+        if (q < 0) continue;
+        uint4* d = dst + (size_t)q * nvec;
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (vb + 32 * u < nvec) __stcs(d + vb + 32 * u, val[u]);
       }
-      a.inverse_perm[s] = pos;
-      if (a.drop_mask != nullptr) a.drop_mask[s] = dropped ? 1 : 0;
-      s_pos[p] = pos;
     }
-    __syncthreads();
-
-    // One warp per token row of the group.
-    if (warp < ng) {
-      const int64_t t = t0 + warp;
-      const int* pos = s_pos + warp * a.K;
-      if (FMT == MOE_RD_ROWS_BF16) {
-        const int nvec = a.H >> 3;
-        const uint4* src = reinterpret_cast<const uint4*>(a.x) + (size_t)t * nvec;
-        uint4* dst = reinterpret_cast<uint4*>(a.rows);
-        for (int v0 = 0; v0 < nvec; v0 += 128) {
-          uint4 val[4];
-#pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            const int v = v0 + u * 32 + lane;
-            if (v < nvec) val[u] = __ldg(src + v);
-          }
-          for (int k = 0; k < a.K; ++k) {
-            const int q = pos[k];
-            if (q < 0) continue;
-            uint4* d = dst + (size_t)q * nvec;
-#pragma unroll
-            for (int u = 0; u < 4; ++u) {
-              const int v = v0 + u * 32 + lane;
-              if (v < nvec) __stcs(d + v, val[u]);
-            }
-          }
-        }
-      } else {
-        // 16 elements per lane: 8 lanes share one 128-element scale block.
-        const int n16 = a.H >> 4;
-        const int nb = a.H >> 7;
-        const uint4* src = reinterpret_cast<const uint4*>(a.x) + (size_t)t * (n16 * 2);
-        uint4* dst = reinterpret_cast<uint4*>(a.rows);
-        for (int v0 = 0; v0 < n16; v0 += 32) {
-          const int v = v0 + lane;
-          const bool act = v < n16;
-          uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-          if (act) {
-            lo = __ldg(src + 2 * v);
-            hi = __ldg(src + 2 * v + 1);
-          }
-          float am = fmaxf(amax8(lo), amax8(hi));
-          am = fmaxf(am, __shfl_xor_sync(kFull, am, 4));
-          am = fmaxf(am, __shfl_xor_sync(kFull, am, 2));
-          am = fmaxf(am, __shfl_xor_sync(kFull, am, 1));
-          const float scale = __fmul_rn(fmaxf(am, 1e-30f), 1.0f / 448.0f);
-          const float inv = __fdiv_rn(1.0f, scale);
-          uint4 q;
-          q.x = quant4(lo.x, lo.y, inv);
-          q.y = quant4(lo.z, lo.w, inv);
-          q.z = quant4(hi.x, hi.y, inv);
-          q.w = quant4(hi.z, hi.w, inv);
-          if (act) {
-            for (int k = 0; k < a.K; ++k) {
-              const int r = pos[k];
-              if (r < 0) continue;
-              __stcs(dst + (size_t)r * n16 + v, q);
-              if ((lane & 7) == 0) a.scales[(size_t)r * nb + (v >> 3)] = scale;
-            }
-          }
+  } else {
+    // unit = 512 elements (four 128-element scale blocks): 16 elements per lane,
+    // 8 lanes per scale block
+    const int n16 = a.H >> 4;
+    const int nb = a.H >> 7;
+    const int upr = (n16 + 31) >> 5;
+    const uint4* x4 = reinterpret_cast<const uint4*>(a.x);
+    uint4* dst = reinterpret_cast<uint4*>(a.rows);
+    UnitWalk wk(w0, W, upr);
+    for (; wk.t < a.T; wk.next()) {
+      const int v = wk.c * 32 + lane;
+      const bool act = v < n16;
+      uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+      if (act) {
+        const uint4* src = x4 + (size_t)wk.t * (n16 * 2) + 2 * v;
+        lo = __ldg(src);
+        hi = __ldg(src + 1);
+      }
+      float am = fmaxf(amax8(lo), amax8(hi));
+      am = fmaxf(am, __shfl_xor_sync(kFull, am, 4));
+      am = fmaxf(am, __shfl_xor_sync(kFull, am, 2));
+      am = fmaxf(am, __shfl_xor_sync(kFull, am, 1));
+      const float scale = __fmul_rn(fmaxf(am, 1e-30f), 1.0f / 448.0f);
+      const float inv = __fdiv_rn(1.0f, scale);
+      uint4 q;
+      q.x = quant4(lo.x, lo.y, inv);
+      q.y = quant4(lo.z, lo.w, inv);
+      q.z = quant4(hi.x, hi.y, inv);
+      q.w = quant4(hi.z, hi.w, inv);
+      if (act) {
+        const int32_t* pos = a.inverse_perm + (size_t)wk.t * a.K;
+        for (int k = 0; k < a.K; ++k) {
+          const int r = __ldg(pos + k);
+          if (r < 0) continue;
+          __stcs(dst + (size_t)r * n16 + v, q);
+          if ((lane & 7) == 0) a.scales[(size_t)r * nb + (v >> 3)] = scale;
         }
       }
     }
   }
+}
+
+int device_sms() {
+  static int cached[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = sms;
+  }
+  return cached[dev];
 }
 
 }  // namespace
@@ -167,35 +208,43 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
                            const int32_t* ids, const int32_t* pair_rank, const int32_t* tile_base,
                            int32_t* status, cudaStream_t s) {
   if (p.T == 0) return cudaSuccess;
+  PositionArgs pa;
+  pa.ids = ids;
+  pa.pair_rank = pair_rank;
+  pa.tile_base = tile_base;
+  pa.offsets = b.offsets;
+  pa.inverse_perm = b.inverse_perm;
+  pa.drop_mask = b.drop_mask;
+  pa.status = status;
+  pa.P = p.T * p.K;
+  pa.capacity = p.capacity;
+  pa.out_rows = p.out_rows;
+  pa.E = p.E;
+  pa.K = p.K;
+  pa.ntiles = plan.ntiles;
+  positions_kernel<<<(unsigned)((pa.P + 255) / 256), 256, 0, s>>>(pa);
+  count_launch();
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+
   ScatterArgs a;
   a.x = static_cast<const uint16_t*>(b.x);
-  a.ids = ids;
-  a.pair_rank = pair_rank;
-  a.tile_base = tile_base;
-  a.offsets = b.offsets;
   a.inverse_perm = b.inverse_perm;
-  a.drop_mask = b.drop_mask;
   a.rows = b.permuted;
   a.scales = b.scales;
-  a.status = status;
   a.T = p.T;
-  a.capacity = p.capacity;
-  a.out_rows = p.out_rows;
   a.H = p.H;
-  a.E = p.E;
   a.K = p.K;
-  a.ntiles = plan.ntiles;
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  const int64_t ngroups = (p.T + kGroup - 1) / kGroup;
-  const int64_t cap = (int64_t)sms * 16;
-  const unsigned grid = (unsigned)(ngroups < cap ? ngroups : cap);
-  const size_t smem = (size_t)kGroup * p.K * sizeof(int);
-  if (p.rows_format == MOE_RD_ROWS_BF16)
-    scatter_kernel<MOE_RD_ROWS_BF16><<<grid, kScatterThreads, smem, s>>>(a);
+  const bool fp8 = p.rows_format == MOE_RD_ROWS_FP8_E4M3_B128;
+  const int64_t upr = fp8 ? ((p.H >> 4) + 31) >> 5 : ((p.H >> 3) + 127) >> 7;
+  const int64_t units = p.T * upr;
+  const int64_t want = (units + kScatterWarps - 1) / kScatterWarps;
+  const int64_t cap = (int64_t)device_sms() * 8;  // 8 resident blocks of 256 threads per SM
+  const unsigned grid = (unsigned)(want < cap ? want : cap);
+  if (fp8)
+    scatter_kernel<MOE_RD_ROWS_FP8_E4M3_B128><<<grid, kScatterThreads, 0, s>>>(a);
   else
-    scatter_kernel<MOE_RD_ROWS_FP8_E4M3_B128><<<grid, kScatterThreads, smem, s>>>(a);
+    scatter_kernel<MOE_RD_ROWS_BF16><<<grid, kScatterThreads, 0, s>>>(a);
   count_launch();
   return cudaGetLastError();
 }

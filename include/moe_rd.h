@@ -41,10 +41,13 @@ enum { MOE_RD_W_F32 = 0, MOE_RD_W_BF16 = 1 };
 enum { MOE_RD_W_LAYOUT_HE = 0 /* [H,E] row-major */, MOE_RD_W_LAYOUT_EH = 1 /* [E,H] */ };
 enum { MOE_RD_ROWS_BF16 = 0, MOE_RD_ROWS_FP8_E4M3_B128 = 1 };
 enum {
-  MOE_RD_GATE_AUTO = 0,     /* E < 64: warp GEMV; E >= 64 with bf16 weights: tcgen05 */
-  MOE_RD_GATE_SIMT = 1,     /* fixed-order fp32 FMA product, any E */
+  MOE_RD_GATE_AUTO = 0,     /* E <= 32: fused warp GEMV; E >= 64 with bf16 weights: tcgen05;
+                               otherwise the SIMT product */
+  MOE_RD_GATE_SIMT = 1,     /* fixed-order fp32 FMA product, any E (defines the logit bits) */
   MOE_RD_GATE_UMMA = 2,     /* tcgen05/TMEM tiles fed by TMA (bf16 weights, E % 16 == 0, E <= 256) */
-  MOE_RD_GATE_EXTERNAL = 3  /* logits supplied by the caller in router_logits */
+  MOE_RD_GATE_EXTERNAL = 3, /* logits supplied by the caller in router_logits */
+  MOE_RD_GATE_GEMV = 4      /* warp GEMV fused with scoring/top-k (E <= 32, weight fits in
+                               shared memory); same logit bits as MOE_RD_GATE_SIMT */
 };
 enum { MOE_RD_SCATTER_AUTO = 0, MOE_RD_SCATTER_SIMT = 1, MOE_RD_SCATTER_BULK = 2 };
 

@@ -39,6 +39,34 @@ def test_c2_full_size():
     check(t, kw, gate_impl="simt")
 
 
+@pytest.mark.parametrize("name,T,H", [("c1", None, None), ("c2", None, None), ("c2", 1000, 1096), ("c1", 33, 264)])
+def test_fused_gemv_gate_matches_oracle_bit_for_bit(name, T, H):
+    """E <= 32: the default path is the warp GEMV fused with routing; its logits
+    follow the same fixed order, so even the logits are bit-exact."""
+    t, kw = workloads.make(name, T=T, H=H)
+    got, ref = check(t, kw, gate_impl="gemv", return_logits=True)
+    np.testing.assert_array_equal(got["router_logits"].view(np.uint32), ref["logits"].view(np.uint32))
+    check(t, kw)  # auto picks the same kernel
+
+
+@pytest.mark.parametrize("E,wdt,layout", [(5, torch.float32, "HE"), (13, torch.bfloat16, "EH"), (16, torch.bfloat16, "HE"),
+                                          (24, torch.float32, "EH"), (32, torch.bfloat16, "HE")])
+def test_fused_gemv_expert_counts_and_layouts(E, wdt, layout):
+    g = torch.Generator().manual_seed(E)
+    T, H = 500, 520
+    w = (torch.randn(H, E, generator=g) * 0.1).to(wdt)
+    t = dict(x=torch.randn(T, H, generator=g).to(torch.bfloat16), w=w, bias=torch.randn(E, generator=g) * 0.1)
+    kw = dict(top_k=min(4, E), bias_mode="logit", score_fn="softmax")
+    ref = _util.run_oracle(t, kw)
+    if layout == "EH":
+        t = dict(t, w=w.t().contiguous())
+        kw = dict(kw, w_layout="EH")
+    for impl in ("gemv", "simt"):
+        got = _util.to_np(_util.run_gpu(t, kw, gate_impl=impl, return_logits=True))
+        _util.assert_parity(got, ref)
+        np.testing.assert_array_equal(got["router_logits"].view(np.uint32), ref["logits"].view(np.uint32))
+
+
 def test_c3_full_size_with_capacity_drops():
     t, kw = workloads.make("c3")
     got, ref = check(t, kw, gate_impl="simt")
@@ -165,7 +193,7 @@ def test_device_status_stays_clean_and_launches_are_counted():
     before = _cabi.launch_count()
     t, kw = workloads.make("c1")
     _util.run_gpu(t, kw)
-    assert _cabi.launch_count() - before >= 4
+    assert _cabi.launch_count() - before >= 4  # fused gate+route, scan, positions, scatter
 
 
 def test_round_trip_property_at_full_size():
