@@ -60,6 +60,10 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
                            const int32_t* ids, const int32_t* pair_rank, const int32_t* tile_base,
                            int32_t* status, cudaStream_t s);
 bool umma_available();
+cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
+                                const float* partial, int nsplit, const float* logit_bias,
+                                float* logits_out, int32_t* ids, int32_t* pair_rank,
+                                int32_t* tile_base, cudaStream_t s);
 bool gemv_eligible(const moe_rd_params& p);
 cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                               float* logits_out, int32_t* ids, int32_t* pair_rank,

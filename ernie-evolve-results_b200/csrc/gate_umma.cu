@@ -1,15 +1,368 @@
-// Placeholder translation unit: the tcgen05 gate product is added separately.
+// Gate logits on the 5th-generation tensor cores: D[128 tokens, E] (fp32, in
+// TMEM) += x[128, 64] * W^T[64, E] per 64-wide K block, operands staged in
+// shared memory by TMA (no multicast), MMAs issued by one thread with
+// tcgen05.mma, accumulator read back with tcgen05.ld.
+//
+// Replaces the library router GEMM of the reference (cublasGemmEx,
+// kernel.cu:4327-4339; the reference ships no hand-written tcgen05 code for
+// it).  One CTA owns one 128-token tile and one K split; it writes raw fp32
+// partial products [split][T][E]; the routing kernel adds the splits in a fixed
+// order (plus the logit bias), so the result does not depend on scheduling.
+//
+// Roles (192 threads): warp 0 = TMA producer, warp 1 = MMA issuer, warps 2..5 =
+// epilogue (a warp may only touch TMEM lanes 32*(warp%4)..+31, and 2,3,4,5 mod 4
+// cover all four quarters).  Every mbarrier wait is bounded: on expiry the
+// kernel records a status code, raises a CTA-wide abort flag, skips the
+// remaining work, frees its TMEM and returns.
+#include <cuda.h>
+
 #include "common.cuh"
 
 namespace moe_rd {
+namespace {
 
-bool umma_available() { return false; }
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;   // 64 bf16 = 128 bytes = one swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 20;
 
-cudaError_t init_umma_attributes() { return cudaSuccess; }
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
 
-cudaError_t launch_gate_umma(const moe_rd_params&, const moe_rd_buffers&, const Plan&, void*,
-                             float*, float*, int32_t*, cudaStream_t) {
-  return cudaErrorNotSupported;
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+// Bounded wait; false when the limit ran out or another role already aborted.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((it & 1023u) == 1023u && *abort_flag) return false;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                            uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+
+// K-major operand tile with 128-byte swizzle: rows of 128 bytes, groups of 8
+// rows 1024 bytes apart (stride byte offset), leading byte offset unused (1).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                         uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+               : "memory");
+}
+
+struct UmmaArgs {
+  float* partial;  // [ksplit][T][E]
+  int32_t* status;
+  int64_t T;
+  int E, kblocks, ksplit, stages, tmem_cols;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                 const UmmaArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  // 1024-byte alignment for the swizzled tiles
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t a_bytes = kBlockM * kBlockK * 2;
+  const uint32_t b_bytes = (uint32_t)a.E * kBlockK * 2;
+  const uint32_t stage_bytes = a_bytes + b_bytes;
+  unsigned char* tail = smem + (size_t)a.stages * stage_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
+  uint64_t* empty_bar = full_bar + a.stages;
+  uint64_t* accum_bar = empty_bar + a.stages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int mt = blockIdx.x, ks = blockIdx.y;
+  const int kb0 = (int)((int64_t)ks * a.kblocks / a.ksplit);
+  const int kb1 = (int)((int64_t)(ks + 1) * a.kblocks / a.ksplit);
+  const int nkb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(smem_u32(full_bar + s), 1);
+      mbar_init(smem_u32(empty_bar + s), 1);
+    }
+    mbar_init(smem_u32(accum_bar), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)a.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % a.stages;
+        const uint32_t use = (uint32_t)(i / a.stages);
+        if (!mbar_wait(smem_u32(empty_bar + s), (use & 1u) ^ 1u, abort_flag)) {
+          if (!*abort_flag) report(a.status, 101, mt, i);
+          *abort_flag = 1;
+          break;
+        }
+        const uint32_t fb = smem_u32(full_bar + s);
+        mbar_expect_tx(fb, stage_bytes);
+        unsigned char* st = smem + (size_t)s * stage_bytes;
+        tma_load_2d(smem_u32(st), &map_x, (kb0 + i) * kBlockK, mt * kBlockM, fb);
+        tma_load_2d(smem_u32(st + a_bytes), &map_w, (kb0 + i) * kBlockK, 0, fb);
+        issued = i + 1;
+      }
+      if (*abort_flag) {
+        // Do not leave the CTA while bulk copies into its shared memory are in
+        // flight: wait (bounded) for the barriers of the last `stages` loads.
+        volatile int never = 0;
+        for (int j = issued > a.stages ? issued - a.stages : 0; j < issued; ++j)
+          mbar_wait(smem_u32(full_bar + j % a.stages), (uint32_t)(j / a.stages) & 1u, &never);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.E >> 3) << 17) |
+                             ((uint32_t)(kBlockM >> 4) << 24);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % a.stages;
+        const uint32_t use = (uint32_t)(i / a.stages);
+        if (!mbar_wait(smem_u32(full_bar + s), use & 1u, abort_flag)) {
+          if (!*abort_flag) report(a.status, 102, mt, i);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        unsigned char* st = smem + (size_t)s * stage_bytes;
+        const uint64_t da = make_desc(smem_u32(st));
+        const uint64_t db = make_desc(smem_u32(st + a_bytes));
+#pragma unroll
+        for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+          // advance 16 elements = 32 bytes inside the 128-byte swizzle row
+          const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);
+          umma_f16(tmem_base, da + step, db + step, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit(smem_u32(empty_bar + s));  // frees the stage once these MMAs have read it
+      }
+      if (ok) umma_commit(smem_u32(accum_bar));
+    }
+  } else {
+    // epilogue: TMEM lane = token row of the tile
+    const int q = warp & 3;
+    bool ok = mbar_wait(smem_u32(accum_bar), 0u, abort_flag);
+    ok = __all_sync(kFull, ok);
+    if (!ok) {
+      if (lane == 0 && !*abort_flag) report(a.status, 103, mt, ks);
+      *abort_flag = 1;
+    } else {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int64_t row = (int64_t)mt * kBlockM + q * 32 + lane;
+      float* out = a.partial + ((size_t)ks * a.T + (row < a.T ? row : 0)) * a.E;
+      for (int c = 0; c < a.E; c += 32) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c;
+        if (a.E - c >= 32) {
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+              "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+              "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+                "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+                "=r"(r[31])
+              : "r"(taddr)
+              : "memory");
+        } else {
+          // E % 32 == 16: the last 16 columns
+#pragma unroll
+          for (int i = 16; i < 32; ++i) r[i] = 0u;
+          asm volatile(
+              "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+              "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+                "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+              : "r"(taddr)
+              : "memory");
+        }
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < a.T) {
+          const int n = a.E - c >= 32 ? 32 : 16;
+          float4* o4 = reinterpret_cast<float4*>(out + c);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (4 * i < n)
+              o4[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                  __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)a.tmem_cols)
+                 : "memory");
+  }
+}
+
+// W[H,E] -> Wt[E,H] (bf16), 32x32 tiles through shared memory.
+__global__ void __launch_bounds__(256) transpose_w_kernel(const uint16_t* __restrict__ w,
+                                                          uint16_t* __restrict__ wt, int H, int E) {
+  __shared__ uint16_t tile[32][33];
+  const int h0 = blockIdx.x * 32, e0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int r = ty; r < 32; r += 8) {
+    const int h = h0 + r, e = e0 + tx;
+    tile[r][tx] = (h < H && e < E) ? w[(size_t)h * E + e] : (uint16_t)0;
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int e = e0 + r, h = h0 + tx;
+    if (e < E && h < H) wt[(size_t)e * H + h] = tile[tx][r];
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// rows x cols bf16, row-major; box = box_rows x 64 columns, 128-byte swizzle.
+bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {cols * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)kBlockK, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+            estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int pick_stages(int E) {
+  const int stage = kBlockM * kBlockK * 2 + E * kBlockK * 2;
+  int s = (200 * 1024) / stage;
+  return s > 8 ? 8 : (s < 2 ? 2 : s);
+}
+
+size_t umma_smem_bytes(int E, int stages) {
+  return (size_t)stages * (kBlockM * kBlockK * 2 + E * kBlockK * 2) + (2 * stages + 1) * 8 + 16 + 1024;
+}
+
+}  // namespace
+
+bool umma_available() { return true; }
+
+cudaError_t init_umma_attributes() {
+  return cudaFuncSetAttribute(gate_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              227 * 1024);
+}
+
+cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
+                             void* wt, float* partial, float* logits, int32_t* status,
+                             cudaStream_t s) {
+  (void)logits;
+  const uint16_t* w_eh = static_cast<const uint16_t*>(b.gate_w);
+  if (p.w_layout == MOE_RD_W_LAYOUT_HE) {
+    const dim3 grid((unsigned)((p.H + 31) / 32), (unsigned)((p.E + 31) / 32));
+    transpose_w_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(b.gate_w),
+                                            static_cast<uint16_t*>(wt), p.H, p.E);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    w_eh = static_cast<const uint16_t*>(wt);
+  }
+  CUtensorMap map_x, map_w;
+  if (!make_map(&map_x, b.x, (uint64_t)p.T, (uint64_t)p.H, kBlockM) ||
+      !make_map(&map_w, w_eh, (uint64_t)p.E, (uint64_t)p.H, (uint32_t)p.E))
+    return cudaErrorInvalidValue;
+  UmmaArgs a;
+  a.partial = partial;
+  a.status = status;
+  a.T = p.T;
+  a.E = p.E;
+  a.kblocks = p.H / kBlockK;
+  a.ksplit = plan.ksplit;
+  a.stages = pick_stages(p.E);
+  int cols = 32;
+  while (cols < p.E) cols <<= 1;
+  a.tmem_cols = cols;
+  const dim3 grid((unsigned)((p.T + kBlockM - 1) / kBlockM), (unsigned)plan.ksplit);
+  gate_umma_kernel<<<grid, kThreads, umma_smem_bytes(p.E, a.stages), s>>>(map_x, map_w, a);
+  count_launch();
+  return cudaGetLastError();
 }
 
 }  // namespace moe_rd

@@ -72,7 +72,17 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_route_kernel(const GemvArgs
 
   // ---- stage the gate weight: element (h, e) of 16-byte unit u = e*WB/16 goes to
   //      unit index ((c*8 + j)*U + u)*32 + l  with h = 256c + 8l + j.
-  {
+  if (g.w_layout == MOE_RD_W_LAYOUT_HE && a.E == EB) {
+    // A weight row is U whole 16-byte units, contiguous in memory: move units.
+    const uint4* w4 = static_cast<const uint4*>(g.w);
+    const int total = nchunk * 256 * U;
+    const int live = g.H * U;
+    for (int idx = tid; idx < total; idx += kGemvThreads) {
+      const int h = idx / U, u = idx - h * U;
+      const int c = h >> 8, l = (h >> 3) & 31, j = h & 7;
+      s_w[((c * 8 + j) * U + u) * 32 + l] = idx < live ? __ldg(w4 + idx) : make_uint4(0, 0, 0, 0);
+    }
+  } else {
     const int Hp = nchunk * 256;
     const int total = Hp * EB;
     for (int idx = tid; idx < total; idx += kGemvThreads) {

@@ -39,12 +39,21 @@ int make_plan(const moe_rd_params& p, Plan* plan) {
   if (gate == MOE_RD_GATE_GEMV && !gemv_eligible(p)) return MOE_RD_E_UNSUPPORTED;
   plan->gate = gate;
   plan->scatter = p.scatter_impl == MOE_RD_SCATTER_AUTO ? MOE_RD_SCATTER_SIMT : p.scatter_impl;
-  // Split K so that about two CTAs per SM are in flight (148 SMs).
+  // One CTA per SM (148): split K by the power of two that fills the last wave
+  // best; ties go to the smaller split (less partial-sum traffic).
   int ksplit = 1;
   if (gate == MOE_RD_GATE_UMMA) {
     const int64_t mtiles = (p.T + 127) / 128;
     const int kblocks = p.H / 64;
-    while (ksplit < 8 && mtiles * ksplit * 2 <= 296 && kblocks / (ksplit * 2) >= 8) ksplit *= 2;
+    double best = -1.0;
+    for (int s = 1; s <= 8 && kblocks / s >= 4; s *= 2) {
+      const int64_t ctas = mtiles * s;
+      const double util = (double)ctas / (double)(((ctas + 147) / 148) * 148);
+      if (util > best + 1e-9) {
+        best = util;
+        ksplit = s;
+      }
+    }
   }
   plan->ksplit = ksplit;
   return MOE_RD_OK;
@@ -64,8 +73,7 @@ void carve(const moe_rd_params& p, const Plan& plan, bool need_logits, bool need
   if (plan.gate == MOE_RD_GATE_UMMA && p.w_layout == MOE_RD_W_LAYOUT_HE)
     o += up256((size_t)p.E * p.H * 2);
   w->partial = o;
-  if (plan.gate == MOE_RD_GATE_UMMA && plan.ksplit > 1)
-    o += up256((size_t)plan.ksplit * p.T * p.E * 4);
+  if (plan.gate == MOE_RD_GATE_UMMA) o += up256((size_t)plan.ksplit * p.T * p.E * 4);
   w->total = o;
 }
 
@@ -201,8 +209,7 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
     return MOE_RD_E_SHAPE;
 
   // The fused GEMV keeps logits in shared memory; it writes them out only on request.
-  const bool need_logits = plan.gate != MOE_RD_GATE_EXTERNAL && plan.gate != MOE_RD_GATE_GEMV &&
-                           b->router_logits == nullptr;
+  const bool need_logits = plan.gate == MOE_RD_GATE_SIMT && b->router_logits == nullptr;
   const bool need_ids = b->expert_ids == nullptr;
   Workspace w;
   carve(*p, plan, need_logits, need_ids, &w);
@@ -233,6 +240,10 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   if (p->T > 0) {
     if (plan.gate == MOE_RD_GATE_GEMV)
       MOE_RD_CUDA(launch_gemv_route(*p, *b, plan, b->router_logits, ids, pair_rank, tile_base, s));
+    else if (plan.gate == MOE_RD_GATE_UMMA)
+      MOE_RD_CUDA(launch_route_splits(*p, *b, plan, reinterpret_cast<float*>(ws + w.partial),
+                                      plan.ksplit, b->logit_bias, b->router_logits, ids, pair_rank,
+                                      tile_base, s));
     else
       MOE_RD_CUDA(launch_route(*p, *b, plan, logits, ids, pair_rank, tile_base, ticket, status, s));
   }

@@ -7,7 +7,7 @@
 namespace moe_rd {
 namespace {
 
-constexpr int kRouteThreads = 256;
+constexpr int kRouteThreads = 32 * kTile;  // one warp per token of the tile
 
 template <int EPL>
 __global__ void __launch_bounds__(kRouteThreads) route_kernel(const RouteArgs a) {
@@ -22,12 +22,20 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const RouteArgs a)
   const int ntok = (int)min((int64_t)kTile, a.T - t0);
 
   for (int tl = warp; tl < ntok; tl += nwarps) {
-    const float* zr = a.logits + (size_t)(t0 + tl) * a.E;
+    const size_t row = (size_t)(t0 + tl) * a.E;
     float z[EPL];
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
       const int e = lane + 32 * i;
-      z[i] = e < a.E ? __ldg(zr + e) : 0.0f;
+      float v = 0.0f;
+      if (e < a.E) {
+        v = __ldg(a.logits + row + e);
+        for (int sp = 1; sp < a.nsplit; ++sp)
+          v = __fadd_rn(v, __ldg(a.logits + (size_t)sp * a.T * a.E + row + e));
+        if (a.logit_bias != nullptr) v = __fadd_rn(v, __ldg(a.logit_bias + e));
+        if (a.logits_out != nullptr) a.logits_out[row + e] = v;
+      }
+      z[i] = v;
     }
     int mysel;
     float myw;
@@ -127,6 +135,9 @@ void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan
                      const float* logits, int32_t* ids, int32_t* pair_rank, int32_t* tile_base,
                      RouteArgs* a) {
   a->logits = logits;
+  a->logit_bias = nullptr;
+  a->logits_out = nullptr;
+  a->nsplit = 1;
   a->select_bias = b.select_bias;
   a->ids = ids;
   a->weights = b.combine_weights;
@@ -151,8 +162,18 @@ cudaError_t launch_route(const moe_rd_params& p, const moe_rd_buffers& b, const 
                          int32_t* ticket, int32_t* status, cudaStream_t s) {
   (void)status;
   (void)ticket;
+  return launch_route_splits(p, b, plan, logits, 1, nullptr, nullptr, ids, pair_rank, tile_base, s);
+}
+
+cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
+                                const float* partial, int nsplit, const float* logit_bias,
+                                float* logits_out, int32_t* ids, int32_t* pair_rank,
+                                int32_t* tile_base, cudaStream_t s) {
   RouteArgs a;
-  fill_route_args(p, b, plan, logits, ids, pair_rank, tile_base, &a);
+  fill_route_args(p, b, plan, partial, ids, pair_rank, tile_base, &a);
+  a.nsplit = nsplit;
+  a.logit_bias = logit_bias;
+  a.logits_out = logits_out;
   const size_t smem = tile_hist_smem(p.K, p.E);
   const dim3 grid((unsigned)plan.ntiles);
   if (p.E <= 32)

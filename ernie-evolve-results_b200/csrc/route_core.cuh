@@ -24,7 +24,10 @@
 namespace moe_rd {
 
 struct RouteArgs {
-  const float* logits;       // [T,E] (unused by the fused gate kernel)
+  const float* logits;       // [nsplit][T,E] (unused by the fused gate kernel)
+  const float* logit_bias;   // [E] added after the splits are summed, or null
+  float* logits_out;         // [T,E] final logits for the caller, or null
+  int nsplit;                // number of K-split partial products to add, in order
   const float* select_bias;  // [E] or null
   int32_t* ids;              // [T,K]
   float* weights;            // [T,K]
