@@ -15,7 +15,7 @@
 
 namespace moe_rd {
 
-constexpr int kTile = 32;    // tokens per routing tile (unit of the deterministic slot order)
+constexpr int kTile = 64;    // tokens per counting tile (granularity of the expert histogram)
 constexpr int kMaxE = 256;
 constexpr int kMaxK = 32;
 constexpr unsigned kFull = 0xffffffffu;
@@ -23,12 +23,13 @@ constexpr unsigned kFull = 0xffffffffu;
 // Workspace carving, computed identically by moe_rd_workspace_bytes and by
 // the call itself.  All offsets are multiples of 256 bytes.
 struct Workspace {
-  size_t status;       // int32[8]  device status block
-  size_t ticket;       // int32[8]  scan ticket counter
+  size_t status;       // int32[8]  device status block            } cleared by one
+  size_t ticket;       // int32[8]  scan ticket counter            } memset at the
+  size_t tile_base;    // int32[E*ntiles] per-tile counts, scanned } start of a call
+                       //           in place to bases
+  size_t zero_bytes;   // length of that cleared prefix
   size_t counts;       // int32[E]  pairs per expert before dropping
   size_t logits;       // float[T*E] when the caller passes no router_logits
-  size_t tile_base;    // int32[E*ntiles] per-tile counts, scanned in place to bases
-  size_t pair_rank;    // int32[T*K] rank of a pair inside its tile and expert
   size_t ids;          // int32[T*K] when the caller passes no expert_ids
   size_t wt;           // bf16[E*H]  gate weight in [E,H] order for the tensor-core gate
   size_t partial;      // float[S*T*E] split-K partial logits of the tensor-core gate
@@ -52,22 +53,20 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
                              void* wt, float* partial, float* logits, int32_t* status,
                              cudaStream_t s);
 cudaError_t launch_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                         const float* logits, int32_t* ids, int32_t* pair_rank, int32_t* tile_base,
-                         int32_t* ticket, int32_t* status, cudaStream_t s);
+                         const float* logits, int32_t* ids, int32_t* tile_base, cudaStream_t s);
+cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
+                                const float* partial, int nsplit, const float* logit_bias,
+                                float* logits_out, int32_t* ids, int32_t* tile_base,
+                                cudaStream_t s);
+cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
+                              float* logits_out, int32_t* ids, int32_t* tile_base, cudaStream_t s);
 cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                         int32_t* tile_base, int32_t* counts, int32_t* ticket, cudaStream_t s);
 cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                           const int32_t* ids, const int32_t* pair_rank, const int32_t* tile_base,
-                           int32_t* status, cudaStream_t s);
+                           const int32_t* ids, const int32_t* tile_base, int32_t* status,
+                           cudaStream_t s);
 bool umma_available();
-cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                                const float* partial, int nsplit, const float* logit_bias,
-                                float* logits_out, int32_t* ids, int32_t* pair_rank,
-                                int32_t* tile_base, cudaStream_t s);
 bool gemv_eligible(const moe_rd_params& p);
-cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                              float* logits_out, int32_t* ids, int32_t* pair_rank,
-                              int32_t* tile_base, cudaStream_t s);
 void count_launch(int n = 1);
 
 // ---------------------------------------------------------------------------

@@ -1,6 +1,6 @@
 // Warp-level GEMV gate for few experts (E <= 32) fused with scoring, top-K and
-// the tile histogram: one kernel from hidden states to expert ids, weights and
-// in-tile ranks.
+// the expert histogram: one kernel from hidden states to expert ids, weights
+// and per-tile expert counts.
 //
 // Replaces wsplit_kernel + the router GEMM + topk_kernel of the reference
 // (kernel.cu:1786-1824, 4327-4339, 1829-1920) where the expert count is far
@@ -56,16 +56,9 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_route_kernel(const GemvArgs
   constexpr int U = EB * WB / 16;                  // 16-byte units per weight row
   constexpr int TPW = 32 / EB;                     // tokens a warp carries at once
   constexpr int NP = EB / 2;                       // accumulator pairs per token
-  constexpr int PASSES = kTile / (kGemvWarps * TPW);
-  static_assert(PASSES * kGemvWarps * TPW == kTile, "tile must be whole passes");
 
   extern __shared__ __align__(16) unsigned char smem[];
-  const size_t wbytes = staged_w_bytes(g.H, EB, WB);
   uint4* s_w = reinterpret_cast<uint4*>(smem);
-  float* s_z = reinterpret_cast<float*>(smem + wbytes);                       // [kTile][EB]
-  int32_t* s_ids = reinterpret_cast<int32_t*>(smem + wbytes + kTile * EB * 4);  // [kTile*K]
-  uint16_t* s_cc =
-      reinterpret_cast<uint16_t*>(smem + wbytes + kTile * EB * 4 + (size_t)kTile * a.K * 4);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nchunk = (g.H + 255) >> 8;
@@ -108,130 +101,123 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_route_kernel(const GemvArgs
   }
   __syncthreads();
 
-  for (int tile = blockIdx.x; tile < a.ntiles; tile += gridDim.x) {
-    const int64_t t0 = (int64_t)tile * kTile;
-    const int ntok = (int)min((int64_t)kTile, a.T - t0);
+  // A unit = TPW consecutive tokens carried by one warp.  Block b owns the
+  // contiguous unit range [U*b/B, U*(b+1)/B), so with B a multiple of the SM
+  // count every SM gets the same work to within one unit.
+  const int64_t units = (a.T + TPW - 1) / TPW;
+  const int64_t ulo = units * blockIdx.x / gridDim.x;
+  const int64_t uhi = units * (blockIdx.x + 1) / gridDim.x;
+  for (int64_t unit = ulo + warp; unit < uhi; unit += kGemvWarps) {
+    const int64_t tb = unit * TPW;
+    const uint4* xr[TPW];
+#pragma unroll
+    for (int i = 0; i < TPW; ++i) {
+      const int64_t t = min(tb + i, a.T - 1);  // clamp: rows past T are computed, not stored
+      xr[i] = reinterpret_cast<const uint4*>(g.x + (size_t)t * g.H);
+    }
+    u64 acc[TPW][NP];
+#pragma unroll
+    for (int i = 0; i < TPW; ++i)
+#pragma unroll
+      for (int q = 0; q < NP; ++q) acc[i][q] = 0ull;
 
-    for (int pass = 0; pass < PASSES; ++pass) {
-      const int tl0 = (pass * kGemvWarps + warp) * TPW;
-      const uint4* xr[TPW];
+    uint4 xn[TPW];
 #pragma unroll
-      for (int i = 0; i < TPW; ++i) {
-        const int64_t t = min(t0 + tl0 + i, a.T - 1);  // clamp: rows past T are computed, not stored
-        xr[i] = reinterpret_cast<const uint4*>(g.x + (size_t)t * g.H);
+    for (int i = 0; i < TPW; ++i) xn[i] = make_uint4(0, 0, 0, 0);
+    if (lane * 8 < g.H) {
+#pragma unroll
+      for (int i = 0; i < TPW; ++i) xn[i] = __ldg(xr[i] + lane);
+    }
+    for (int c = 0; c < nchunk; ++c) {
+      const int h0 = c * 256 + lane * 8;
+      uint4 xv[TPW];
+#pragma unroll
+      for (int i = 0; i < TPW; ++i) xv[i] = xn[i];
+      if (c + 1 < nchunk && h0 + 256 < g.H) {
+#pragma unroll
+        for (int i = 0; i < TPW; ++i) xn[i] = __ldg(xr[i] + ((h0 + 256) >> 3));
       }
-      u64 acc[TPW][NP];
+      if (h0 < g.H) {
+        const uint4* wrow = s_w + (size_t)c * 8 * U * 32 + lane;
 #pragma unroll
-      for (int i = 0; i < TPW; ++i)
+        for (int j = 0; j < 8; ++j) {
+          u64 wp[NP];
 #pragma unroll
-        for (int q = 0; q < NP; ++q) acc[i][q] = 0ull;
-
-      uint4 xn[TPW];
-#pragma unroll
-      for (int i = 0; i < TPW; ++i) xn[i] = make_uint4(0, 0, 0, 0);
-      if (lane * 8 < g.H) {
-#pragma unroll
-        for (int i = 0; i < TPW; ++i) xn[i] = __ldg(xr[i] + lane);
-      }
-      for (int c = 0; c < nchunk; ++c) {
-        const int h0 = c * 256 + lane * 8;
-        uint4 xv[TPW];
-#pragma unroll
-        for (int i = 0; i < TPW; ++i) xv[i] = xn[i];
-        if (c + 1 < nchunk && h0 + 256 < g.H) {
-#pragma unroll
-          for (int i = 0; i < TPW; ++i) xn[i] = __ldg(xr[i] + ((h0 + 256) >> 3));
-        }
-        if (h0 < g.H) {
-          const uint4* wrow = s_w + (size_t)c * 8 * U * 32 + lane;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            u64 wp[NP];
-#pragma unroll
-            for (int u = 0; u < U; ++u) {
-              const uint4 v = wrow[(j * U + u) * 32];
-              if (WD == MOE_RD_W_BF16) {
-                wp[4 * u + 0] = bf16x2_to_f32x2(v.x);
-                wp[4 * u + 1] = bf16x2_to_f32x2(v.y);
-                wp[4 * u + 2] = bf16x2_to_f32x2(v.z);
-                wp[4 * u + 3] = bf16x2_to_f32x2(v.w);
-              } else {
-                wp[2 * u + 0] = (u64)v.x | ((u64)v.y << 32);
-                wp[2 * u + 1] = (u64)v.z | ((u64)v.w << 32);
-              }
+          for (int u = 0; u < U; ++u) {
+            const uint4 v = wrow[(j * U + u) * 32];
+            if (WD == MOE_RD_W_BF16) {
+              wp[4 * u + 0] = bf16x2_to_f32x2(v.x);
+              wp[4 * u + 1] = bf16x2_to_f32x2(v.y);
+              wp[4 * u + 2] = bf16x2_to_f32x2(v.z);
+              wp[4 * u + 3] = bf16x2_to_f32x2(v.w);
+            } else {
+              wp[2 * u + 0] = (u64)v.x | ((u64)v.y << 32);
+              wp[2 * u + 1] = (u64)v.z | ((u64)v.w << 32);
             }
+          }
 #pragma unroll
-            for (int i = 0; i < TPW; ++i) {
-              const uint32_t pk = j < 2 ? xv[i].x : j < 4 ? xv[i].y : j < 6 ? xv[i].z : xv[i].w;
-              const float xf = (j & 1) ? bf16_hi(pk) : bf16_lo(pk);
-              const u64 xx = pack2(xf, xf);
+          for (int i = 0; i < TPW; ++i) {
+            const uint32_t pk = j < 2 ? xv[i].x : j < 4 ? xv[i].y : j < 6 ? xv[i].z : xv[i].w;
+            const float xf = (j & 1) ? bf16_hi(pk) : bf16_lo(pk);
+            const u64 xx = pack2(xf, xf);
 #pragma unroll
-              for (int q = 0; q < NP; ++q) ffma2(acc[i][q], xx, wp[q]);
-            }
+            for (int q = 0; q < NP; ++q) ffma2(acc[i][q], xx, wp[q]);
           }
         }
       }
+    }
 
-      // lane sums -> token logits by the fixed tree; lane e keeps expert e
+    // lane sums -> token logits by the fixed tree; lane e keeps expert e, then
+    // the warp routes the token at once (E <= 32: one expert per lane)
 #pragma unroll
-      for (int i = 0; i < TPW; ++i) {
-        float mine = 0.0f;
+    for (int i = 0; i < TPW; ++i) {
+      float mine = 0.0f;
 #pragma unroll
-        for (int q = 0; q < NP; ++q) {
-          float v0 = lo_of(acc[i][q]), v1 = hi_of(acc[i][q]);
+      for (int q = 0; q < NP; ++q) {
+        float v0 = lo_of(acc[i][q]), v1 = hi_of(acc[i][q]);
 #pragma unroll
-          for (int o = 16; o; o >>= 1) {
-            v0 = __fadd_rn(v0, __shfl_xor_sync(kFull, v0, o));
-            v1 = __fadd_rn(v1, __shfl_xor_sync(kFull, v1, o));
-          }
-          if (lane == 2 * q) mine = v0;
-          if (lane == 2 * q + 1) mine = v1;
+        for (int o = 16; o; o >>= 1) {
+          v0 = __fadd_rn(v0, __shfl_xor_sync(kFull, v0, o));
+          v1 = __fadd_rn(v1, __shfl_xor_sync(kFull, v1, o));
         }
-        const int tl = tl0 + i;
-        if (lane < EB && lane < a.E && tl < ntok) {
+        if (lane == 2 * q) mine = v0;
+        if (lane == 2 * q + 1) mine = v1;
+      }
+      const int64_t t = tb + i;
+      if (t < a.T) {  // warp-uniform
+        if (lane < a.E) {
           if (g.logit_bias != nullptr) mine = __fadd_rn(mine, __ldg(g.logit_bias + lane));
-          s_z[tl * EB + lane] = mine;
-          if (g.logits_out != nullptr) g.logits_out[(size_t)(t0 + tl) * a.E + lane] = mine;
+          if (g.logits_out != nullptr) g.logits_out[(size_t)t * a.E + lane] = mine;
+        } else {
+          mine = 0.0f;
         }
+        float z[1] = {mine};
+        int mysel;
+        float myw;
+        route_token<1>(a, z, lane, mysel, myw);
+        publish_token(a, t, lane, mysel, myw);
       }
     }
-    __syncthreads();
-
-    for (int tl = warp; tl < ntok; tl += kGemvWarps) {
-      float z[1];
-      z[0] = lane < a.E ? s_z[tl * EB + lane] : 0.0f;
-      int mysel;
-      float myw;
-      route_token<1>(a, z, lane, mysel, myw);
-      if (lane < a.K) {
-        const size_t s = (size_t)(t0 + tl) * a.K + lane;
-        a.ids[s] = mysel;
-        a.weights[s] = myw;
-        s_ids[tl * a.K + lane] = mysel;
-      }
-    }
-    __syncthreads();
-    tile_histogram<kGemvThreads>(a, s_ids, s_cc, ntok * a.K, tile, t0);
   }
 }
 
 size_t gemv_smem_bytes(const moe_rd_params& p, int EB) {
   const int wb = p.w_dtype == MOE_RD_W_BF16 ? 2 : 4;
-  return staged_w_bytes(p.H, EB, wb) + (size_t)kTile * EB * 4 + tile_hist_smem(p.K, p.E);
+  return staged_w_bytes(p.H, EB, wb);
 }
 
 int pick_eb(int E) { return E <= 8 ? 8 : E <= 16 ? 16 : 32; }
 
 template <int EB, int WD>
-cudaError_t launch_t(const moe_rd_params& p, const GemvArgs& g, const RouteArgs& a, int ntiles,
+cudaError_t launch_t(const moe_rd_params& p, const GemvArgs& g, const RouteArgs& a,
                      cudaStream_t s) {
   const size_t smem = gemv_smem_bytes(p, EB);
-  int dev = 0, sms = 148;
-  cudaGetDevice(&dev);
-  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   // Two blocks per SM when shared memory allows (registers allow no more).
   const int per_sm = smem * 2 + 2048 <= (size_t)kMaxDynSmem ? 2 : 1;
-  const int grid = ntiles < sms * per_sm ? ntiles : sms * per_sm;
+  const int64_t units = (p.T + 32 / EB - 1) / (32 / EB);
+  const int64_t need = (units + kGemvWarps - 1) / kGemvWarps;
+  const int64_t cap = (int64_t)device_sms() * per_sm;
+  const int grid = (int)(need < cap ? need : cap);
   gemv_route_kernel<EB, WD><<<grid, kGemvThreads, smem, s>>>(g, a);
   count_launch();
   return cudaGetLastError();
@@ -245,8 +231,7 @@ bool gemv_eligible(const moe_rd_params& p) {
 }
 
 cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                              float* logits_out, int32_t* ids, int32_t* pair_rank,
-                              int32_t* tile_base, cudaStream_t s) {
+                              float* logits_out, int32_t* ids, int32_t* tile_base, cudaStream_t s) {
   GemvArgs g;
   g.x = static_cast<const uint16_t*>(b.x);
   g.w = b.gate_w;
@@ -255,17 +240,17 @@ cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, c
   g.H = p.H;
   g.w_layout = p.w_layout;
   RouteArgs a;
-  fill_route_args(p, b, plan, nullptr, ids, pair_rank, tile_base, &a);
+  fill_route_args(p, b, plan, nullptr, ids, tile_base, &a);
   const int eb = pick_eb(p.E);
   const bool bf = p.w_dtype == MOE_RD_W_BF16;
   if (eb == 8)
-    return bf ? launch_t<8, MOE_RD_W_BF16>(p, g, a, plan.ntiles, s)
-              : launch_t<8, MOE_RD_W_F32>(p, g, a, plan.ntiles, s);
+    return bf ? launch_t<8, MOE_RD_W_BF16>(p, g, a, s)
+              : launch_t<8, MOE_RD_W_F32>(p, g, a, s);
   if (eb == 16)
-    return bf ? launch_t<16, MOE_RD_W_BF16>(p, g, a, plan.ntiles, s)
-              : launch_t<16, MOE_RD_W_F32>(p, g, a, plan.ntiles, s);
-  return bf ? launch_t<32, MOE_RD_W_BF16>(p, g, a, plan.ntiles, s)
-            : launch_t<32, MOE_RD_W_F32>(p, g, a, plan.ntiles, s);
+    return bf ? launch_t<16, MOE_RD_W_BF16>(p, g, a, s)
+              : launch_t<16, MOE_RD_W_F32>(p, g, a, s);
+  return bf ? launch_t<32, MOE_RD_W_BF16>(p, g, a, s)
+            : launch_t<32, MOE_RD_W_F32>(p, g, a, s);
 }
 
 cudaError_t init_gemv_attributes() {

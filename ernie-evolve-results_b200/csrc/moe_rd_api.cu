@@ -18,6 +18,7 @@ void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 cudaError_t init_route_attributes();
 cudaError_t init_umma_attributes();
 cudaError_t init_gemv_attributes();
+cudaError_t init_scatter_attributes();
 
 static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -64,10 +65,10 @@ void carve(const moe_rd_params& p, const Plan& plan, bool need_logits, bool need
   size_t o = 0;
   w->status = o; o += 256;
   w->ticket = o; o += 256;
+  w->tile_base = o; o += up256((size_t)p.E * plan.ntiles * 4);
+  w->zero_bytes = o;
   w->counts = o; o += up256((size_t)p.E * 4);
   w->logits = o; if (need_logits) o += up256((size_t)p.T * p.E * 4);
-  w->tile_base = o; o += up256((size_t)p.E * plan.ntiles * 4);
-  w->pair_rank = o; o += up256((size_t)p.T * p.K * 4);
   w->ids = o; if (need_ids) o += up256((size_t)p.T * p.K * 4);
   w->wt = o;
   if (plan.gate == MOE_RD_GATE_UMMA && p.w_layout == MOE_RD_W_LAYOUT_HE)
@@ -101,8 +102,6 @@ static int validate(const moe_rd_params* p) {
     return MOE_RD_E_ENUM;
   if (p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128 && p->H % 128 != 0) return MOE_RD_E_SHAPE;
   if (p->capacity < 0 || p->out_rows < 0 || p->out_rows > 0x7fffffff) return MOE_RD_E_SHAPE;
-  // The tile-local pair ranks are kept in 16 bits of shared memory.
-  if ((int64_t)kTile * p->K > 65535) return MOE_RD_E_SHAPE;
   if ((int64_t)p->E * ((p->T + kTile - 1) / kTile) > 0x7fffffff) return MOE_RD_E_TOO_LARGE;
   return MOE_RD_OK;
 }
@@ -125,6 +124,8 @@ static cudaError_t init_device_once() {
   e = init_umma_attributes();
   if (e != cudaSuccess) return e;
   e = init_gemv_attributes();
+  if (e != cudaSuccess) return e;
+  e = init_scatter_attributes();
   if (e != cudaSuccess) return e;
   done[dev] = true;
   return cudaSuccess;
@@ -222,11 +223,10 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   int32_t* counts = reinterpret_cast<int32_t*>(ws + w.counts);
   float* logits = need_logits ? reinterpret_cast<float*>(ws + w.logits) : b->router_logits;
   int32_t* tile_base = reinterpret_cast<int32_t*>(ws + w.tile_base);
-  int32_t* pair_rank = reinterpret_cast<int32_t*>(ws + w.pair_rank);
   int32_t* ids = need_ids ? reinterpret_cast<int32_t*>(ws + w.ids) : b->expert_ids;
 
-  // status block and ticket counter are adjacent: one 512-byte clear.
-  MOE_RD_CUDA(cudaMemsetAsync(ws + w.status, 0, 512, s));
+  // status block, ticket counter and the tile counts are adjacent: one clear.
+  MOE_RD_CUDA(cudaMemsetAsync(ws + w.status, 0, w.zero_bytes, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[0], s));
   if (p->T > 0) {
     if (plan.gate == MOE_RD_GATE_SIMT) {
@@ -239,18 +239,18 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[1], s));
   if (p->T > 0) {
     if (plan.gate == MOE_RD_GATE_GEMV)
-      MOE_RD_CUDA(launch_gemv_route(*p, *b, plan, b->router_logits, ids, pair_rank, tile_base, s));
+      MOE_RD_CUDA(launch_gemv_route(*p, *b, plan, b->router_logits, ids, tile_base, s));
     else if (plan.gate == MOE_RD_GATE_UMMA)
       MOE_RD_CUDA(launch_route_splits(*p, *b, plan, reinterpret_cast<float*>(ws + w.partial),
-                                      plan.ksplit, b->logit_bias, b->router_logits, ids, pair_rank,
-                                      tile_base, s));
+                                      plan.ksplit, b->logit_bias, b->router_logits, ids, tile_base,
+                                      s));
     else
-      MOE_RD_CUDA(launch_route(*p, *b, plan, logits, ids, pair_rank, tile_base, ticket, status, s));
+      MOE_RD_CUDA(launch_route(*p, *b, plan, logits, ids, tile_base, s));
   }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[2], s));
   MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, ticket, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[3], s));
-  MOE_RD_CUDA(launch_scatter(*p, *b, plan, ids, pair_rank, tile_base, status, s));
+  MOE_RD_CUDA(launch_scatter(*p, *b, plan, ids, tile_base, status, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[4], s));
   return MOE_RD_OK;
 }

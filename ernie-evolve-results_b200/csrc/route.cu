@@ -7,22 +7,19 @@
 namespace moe_rd {
 namespace {
 
-constexpr int kRouteThreads = 32 * kTile;  // one warp per token of the tile
+constexpr int kRouteThreads = 512;
+constexpr int kRouteWarps = kRouteThreads / 32;
 
+// One warp per token.  Block b owns the contiguous token range
+// [T*b/B, T*(b+1)/B): with B a multiple of the SM count every SM gets the same
+// number of tokens to within one, whatever T is.
 template <int EPL>
 __global__ void __launch_bounds__(kRouteThreads) route_kernel(const RouteArgs a) {
-  extern __shared__ __align__(16) unsigned char smem[];
-  int32_t* s_ids = reinterpret_cast<int32_t*>(smem);                             // [kTile*K]
-  uint16_t* s_cc = reinterpret_cast<uint16_t*>(smem + (size_t)kTile * a.K * 4);  // [chunks][E]
-
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  constexpr int nwarps = kRouteThreads / 32;
-  const int tile = blockIdx.x;
-  const int64_t t0 = (int64_t)tile * kTile;
-  const int ntok = (int)min((int64_t)kTile, a.T - t0);
-
-  for (int tl = warp; tl < ntok; tl += nwarps) {
-    const size_t row = (size_t)(t0 + tl) * a.E;
+  const int64_t lo = a.T * blockIdx.x / gridDim.x;
+  const int64_t hi = a.T * (blockIdx.x + 1) / gridDim.x;
+  for (int64_t t = lo + warp; t < hi; t += kRouteWarps) {
+    const size_t row = (size_t)t * a.E;
     float z[EPL];
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
@@ -40,15 +37,8 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const RouteArgs a)
     int mysel;
     float myw;
     route_token<EPL>(a, z, lane, mysel, myw);
-    if (lane < a.K) {
-      const size_t s = (size_t)(t0 + tl) * a.K + lane;
-      a.ids[s] = mysel;
-      a.weights[s] = myw;
-      s_ids[tl * a.K + lane] = mysel;
-    }
+    publish_token(a, t, lane, mysel, myw);
   }
-  __syncthreads();
-  tile_histogram<kRouteThreads>(a, s_ids, s_cc, ntok * a.K, tile, t0);
 }
 
 // ---------------------------------------------------------------------------
@@ -131,9 +121,21 @@ scan_kernel(int32_t* __restrict__ tile_base, int32_t* __restrict__ counts,
 
 }  // namespace
 
+int device_sms() {
+  static int cached[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int sms = 148;
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    cached[dev] = sms;
+  }
+  return cached[dev];
+}
+
 void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                     const float* logits, int32_t* ids, int32_t* pair_rank, int32_t* tile_base,
-                     RouteArgs* a) {
+                     const float* logits, int32_t* ids, int32_t* tile_base, RouteArgs* a) {
   a->logits = logits;
   a->logit_bias = nullptr;
   a->logits_out = nullptr;
@@ -141,7 +143,6 @@ void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan
   a->select_bias = b.select_bias;
   a->ids = ids;
   a->weights = b.combine_weights;
-  a->pair_rank = pair_rank;
   a->tile_counts = tile_base;
   a->T = p.T;
   a->E = p.E;
@@ -158,32 +159,32 @@ void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan
 }
 
 cudaError_t launch_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                         const float* logits, int32_t* ids, int32_t* pair_rank, int32_t* tile_base,
-                         int32_t* ticket, int32_t* status, cudaStream_t s) {
-  (void)status;
-  (void)ticket;
-  return launch_route_splits(p, b, plan, logits, 1, nullptr, nullptr, ids, pair_rank, tile_base, s);
+                         const float* logits, int32_t* ids, int32_t* tile_base, cudaStream_t s) {
+  return launch_route_splits(p, b, plan, logits, 1, nullptr, nullptr, ids, tile_base, s);
 }
 
 cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                                 const float* partial, int nsplit, const float* logit_bias,
-                                float* logits_out, int32_t* ids, int32_t* pair_rank,
-                                int32_t* tile_base, cudaStream_t s) {
+                                float* logits_out, int32_t* ids, int32_t* tile_base,
+                                cudaStream_t s) {
   RouteArgs a;
-  fill_route_args(p, b, plan, partial, ids, pair_rank, tile_base, &a);
+  fill_route_args(p, b, plan, partial, ids, tile_base, &a);
   a.nsplit = nsplit;
   a.logit_bias = logit_bias;
   a.logits_out = logits_out;
-  const size_t smem = tile_hist_smem(p.K, p.E);
-  const dim3 grid((unsigned)plan.ntiles);
+  // two resident blocks of 512 threads per SM (<= 64 registers per thread)
+  int64_t nblk = (int64_t)device_sms() * 2;
+  const int64_t need = (p.T + kRouteWarps - 1) / kRouteWarps;
+  if (nblk > need) nblk = need;
+  const dim3 grid((unsigned)nblk);
   if (p.E <= 32)
-    route_kernel<1><<<grid, kRouteThreads, smem, s>>>(a);
+    route_kernel<1><<<grid, kRouteThreads, 0, s>>>(a);
   else if (p.E <= 64)
-    route_kernel<2><<<grid, kRouteThreads, smem, s>>>(a);
+    route_kernel<2><<<grid, kRouteThreads, 0, s>>>(a);
   else if (p.E <= 128)
-    route_kernel<4><<<grid, kRouteThreads, smem, s>>>(a);
+    route_kernel<4><<<grid, kRouteThreads, 0, s>>>(a);
   else
-    route_kernel<8><<<grid, kRouteThreads, smem, s>>>(a);
+    route_kernel<8><<<grid, kRouteThreads, 0, s>>>(a);
   count_launch();
   return cudaGetLastError();
 }
@@ -196,17 +197,6 @@ cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const P
   return cudaGetLastError();
 }
 
-cudaError_t init_route_attributes() {
-  const int max_smem = (int)tile_hist_smem(kMaxK, kMaxE);
-  cudaError_t e;
-  e = cudaFuncSetAttribute(route_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(route_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-  if (e != cudaSuccess) return e;
-  e = cudaFuncSetAttribute(route_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem);
-  if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(route_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              max_smem);
-}
+cudaError_t init_route_attributes() { return cudaSuccess; }
 
 }  // namespace moe_rd

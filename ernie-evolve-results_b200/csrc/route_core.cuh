@@ -13,10 +13,11 @@
 // which selects the same expert.
 //
 // The reference ranks a pair inside its expert with shared and global atomics
-// (dispatch_body, kernel.cu:2155-2158), so its slot order depends on
-// scheduling.  Here a block owns a tile of kTile consecutive tokens, counts
-// every 32 consecutive pairs with __match_any_sync and prefix-sums the counts
-// in pair order: a pair's rank is a pure function of the ids.
+// whose return values become slot positions (dispatch_body,
+// kernel.cu:2155-2158), so its slot order depends on scheduling.  Here the
+// routing kernels only COUNT with atomics: pairs per (expert, tile of kTile
+// consecutive tokens), an integer sum that is the same in any order.  Slot
+// order is decided later, from the ids alone (positions_kernel, scatter.cu).
 #pragma once
 
 #include "common.cuh"
@@ -31,8 +32,7 @@ struct RouteArgs {
   const float* select_bias;  // [E] or null
   int32_t* ids;              // [T,K]
   float* weights;            // [T,K]
-  int32_t* pair_rank;        // [T*K]
-  int32_t* tile_counts;      // [E][ntiles]
+  int32_t* tile_counts;      // [E][ntiles], zeroed before the kernel
   int64_t T;
   int E, K, ntiles;
   int n_groups, topk_groups, group_topk;
@@ -72,13 +72,13 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)
       sc[i] = p;
       part = __fadd_rn(part, p);
     }
-    const float rs = __fdiv_rn(1.0f, warp_tree_sum(part));
+    const float rs = __frcp_rn(warp_tree_sum(part));  // correctly rounded: same bits as 1.0f / s
 #pragma unroll
     for (int i = 0; i < EPL; ++i) sc[i] = __fmul_rn(sc[i], rs);
   } else {
 #pragma unroll
     for (int i = 0; i < EPL; ++i)
-      sc[i] = lane + 32 * i < a.E ? __fdiv_rn(1.0f, __fadd_rn(1.0f, exp_ieee(-z[i]))) : 0.0f;
+      sc[i] = lane + 32 * i < a.E ? __frcp_rn(__fadd_rn(1.0f, exp_ieee(-z[i]))) : 0.0f;
   }
 #pragma unroll
   for (int i = 0; i < EPL; ++i) {
@@ -91,7 +91,25 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)
   if (a.n_groups > 1) {
     const int gs = a.E / a.n_groups;
     float mygs = 0.0f;  // lane g keeps the score of group g
-    if ((gs & 31) == 0 && a.group_topk <= 2) {
+    if (gs == 32 && a.group_topk <= 2) {
+      // Group g is exactly register g of every lane.
+#pragma unroll
+      for (int g = 0; g < EPL; ++g) {
+        if (g < a.n_groups) {
+          const uint32_t l1 = ok[g];
+          const uint32_t m1 = __reduce_max_sync(kFull, l1);
+          float sum = ord_value(m1);
+          if (a.group_topk == 2) {
+            // Second largest = largest once ONE instance of m1 is removed.
+            const unsigned holders = __ballot_sync(kFull, l1 == m1);
+            uint32_t m2 = m1;
+            if (__popc(holders) < 2) m2 = __reduce_max_sync(kFull, l1 == m1 ? 0u : l1);
+            sum = __fadd_rn(sum, ord_value(m2));
+          }
+          if (lane == g) mygs = sum;
+        }
+      }
+    } else if ((gs & 31) == 0 && a.group_topk <= 2) {
       // A group is a whole number of registers: m = gs/32 of them per lane.
       const int m = gs >> 5;
       for (int g = 0; g < a.n_groups; ++g) {
@@ -111,7 +129,6 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)
         const uint32_t m1 = __reduce_max_sync(kFull, l1);
         float sum = ord_value(m1);
         if (a.group_topk == 2) {
-          // Second largest = largest once ONE instance of m1 is removed.
           const unsigned holders = __ballot_sync(kFull, l1 == m1);
           uint32_t m2 = m1;
           if (__popc(holders) < 2) m2 = __reduce_max_sync(kFull, l1 == m1 ? l2 : l1);
@@ -194,57 +211,20 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)
   myw = __fmul_rn(wv, a.routed_scale);
 }
 
-// Shared memory a tile needs for ids + chunk counts.
-__host__ __device__ inline size_t tile_hist_smem(int K, int E) {
-  return (size_t)kTile * K * 4 + (size_t)((kTile * K + 31) / 32) * E * 2 + 16;
-}
-
-// In-tile stable ranks and per-expert tile counts from the ids in s_ids[0..P).
-// Called by every thread of the block after s_ids is complete (a barrier has
-// been passed); s_cc must hold ceil(P/32)*E uint16.  Ends with a barrier.
-template <int NTHREADS>
-__device__ __forceinline__ void tile_histogram(const RouteArgs& a, const int32_t* s_ids,
-                                               uint16_t* s_cc, int P, int tile, int64_t t0) {
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  constexpr int nwarps = NTHREADS / 32;
-  const int nch = (P + 31) >> 5;
-  {
-    uint32_t* z32 = reinterpret_cast<uint32_t*>(s_cc);
-    const int nw = (nch * a.E + 1) >> 1;
-    for (int i = tid; i < nw; i += NTHREADS) z32[i] = 0u;
+// Lanes k < K publish slot k of token t: id, weight, and one count for the
+// (expert, tile) cell.
+__device__ __forceinline__ void publish_token(const RouteArgs& a, int64_t t, int lane, int mysel,
+                                              float myw) {
+  if (lane < a.K) {
+    const size_t s = (size_t)t * a.K + lane;
+    a.ids[s] = mysel;
+    a.weights[s] = myw;
+    atomicAdd(a.tile_counts + (size_t)mysel * a.ntiles + (int)(t / kTile), 1);
   }
-  __syncthreads();
-  // Count every 32 consecutive pairs per expert.
-  for (int c = warp; c < nch; c += nwarps) {
-    const int p = c * 32 + lane;
-    const int e = p < P ? s_ids[p] : -1;
-    const unsigned m = __match_any_sync(kFull, e);
-    if (e >= 0 && (m & ((1u << lane) - 1u)) == 0u) s_cc[c * a.E + e] = (uint16_t)__popc(m);
-  }
-  __syncthreads();
-  // Exclusive prefix over the chunks of each expert, in pair order.
-  for (int e = tid; e < a.E; e += NTHREADS) {
-    int run = 0;
-    for (int c = 0; c < nch; ++c) {
-      const int v = s_cc[c * a.E + e];
-      s_cc[c * a.E + e] = (uint16_t)run;
-      run += v;
-    }
-    a.tile_counts[(size_t)e * a.ntiles + tile] = run;
-  }
-  __syncthreads();
-  for (int c = warp; c < nch; c += nwarps) {
-    const int p = c * 32 + lane;
-    const int e = p < P ? s_ids[p] : -1;
-    const unsigned m = __match_any_sync(kFull, e);
-    if (e >= 0)
-      a.pair_rank[(size_t)t0 * a.K + p] = (int)s_cc[c * a.E + e] + __popc(m & ((1u << lane) - 1u));
-  }
-  __syncthreads();
 }
 
 void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                     const float* logits, int32_t* ids, int32_t* pair_rank, int32_t* tile_base,
-                     RouteArgs* a);
+                     const float* logits, int32_t* ids, int32_t* tile_base, RouteArgs* a);
+int device_sms();
 
 }  // namespace moe_rd

@@ -11,7 +11,9 @@
 // all integers produced by the route and scan kernels, so the slot order is
 // the stable (token, slot) order.  Pairs whose rank inside the expert reaches
 // the capacity get inverse_perm = -1 and are not written.  positions_kernel
-// turns those integers into inverse_perm / drop_mask; scatter_kernel is then a
+// derives rank_in_tile from the ids (replacing the atomic ranks of the
+// reference's dispatch_body, kernel.cu:2155-2158, by a stable count) and
+// writes inverse_perm / drop_mask; scatter_kernel is then a
 // pure streaming kernel whose work units (a 2 KB slice of a bf16 row, or 512
 // elements = four scale blocks of an fp8 row) are dealt to warps grid-stride,
 // so the load is even whatever T, H and K are.
@@ -31,39 +33,80 @@ constexpr int kScatterWarps = kScatterThreads / 32;
 
 struct PositionArgs {
   const int32_t* ids;
-  const int32_t* pair_rank;
   const int32_t* tile_base;  // [E][ntiles], scanned
   const int32_t* offsets;    // [E+1]
   int32_t* inverse_perm;
   uint8_t* drop_mask;
   int32_t* status;
-  int64_t P, capacity, out_rows;
+  int64_t T, capacity, out_rows;
   int E, K, ntiles;
 };
 
-__global__ void __launch_bounds__(256) positions_kernel(const PositionArgs a) {
-  const int64_t s = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  if (s >= a.P) return;
-  const int64_t t = s / a.K;
-  const int e = a.ids[s];
-  int pos = -1;
-  bool dropped = false;
-  if (e < 0 || e >= a.E) {
-    report(a.status, 1, e, (int)s);
-  } else {
-    const int64_t r =
-        (int64_t)a.tile_base[(size_t)e * a.ntiles + (int)(t / kTile)] + a.pair_rank[s];
-    dropped = a.capacity > 0 && r >= a.capacity;
-    if (!dropped) {
-      const int64_t q = (int64_t)a.offsets[e] + r;
-      if (q < 0 || q >= a.out_rows)
-        report(a.status, 2, (int)q, (int)s);
-      else
-        pos = (int)q;
+constexpr int kPosThreads = 256;
+
+// One block per tile of kTile tokens.  The rank of a pair inside its tile and
+// expert is the number of earlier pairs (flat index t*K+k) of the tile with the
+// same expert: every 32 consecutive pairs are counted with __match_any_sync and
+// the per-chunk counts are prefix-summed per expert in pair order.
+__global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionArgs a) {
+  extern __shared__ __align__(16) uint16_t s_cc[];  // [chunks][E]
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  constexpr int nwarps = kPosThreads / 32;
+  const int tile = blockIdx.x;
+  const int64_t t0 = (int64_t)tile * kTile;
+  const int ntok = (int)min((int64_t)kTile, a.T - t0);
+  const int P = ntok * a.K;
+  const int nch = (P + 31) >> 5;
+  const int32_t* ids = a.ids + (size_t)t0 * a.K;
+  {
+    uint32_t* z32 = reinterpret_cast<uint32_t*>(s_cc);
+    const int nw = (nch * a.E + 1) >> 1;
+    for (int i = tid; i < nw; i += kPosThreads) z32[i] = 0u;
+  }
+  __syncthreads();
+  for (int c = warp; c < nch; c += nwarps) {
+    const int p = c * 32 + lane;
+    int e = p < P ? ids[p] : -1;
+    if (e >= a.E) e = -1;
+    const unsigned m = __match_any_sync(kFull, e);
+    if (e >= 0 && (m & ((1u << lane) - 1u)) == 0u) s_cc[c * a.E + e] = (uint16_t)__popc(m);
+  }
+  __syncthreads();
+  for (int e = tid; e < a.E; e += kPosThreads) {
+    int run = 0;
+    for (int c = 0; c < nch; ++c) {
+      const int v = s_cc[c * a.E + e];
+      s_cc[c * a.E + e] = (uint16_t)run;
+      run += v;
     }
   }
-  a.inverse_perm[s] = pos;
-  if (a.drop_mask != nullptr) a.drop_mask[s] = dropped ? 1 : 0;
+  __syncthreads();
+  for (int c = warp; c < nch; c += nwarps) {
+    const int p = c * 32 + lane;
+    const int e_raw = p < P ? ids[p] : -1;
+    const int e = e_raw >= a.E ? -1 : e_raw;
+    const unsigned m = __match_any_sync(kFull, e);
+    if (p >= P) continue;
+    const size_t s = (size_t)t0 * a.K + p;
+    int pos = -1;
+    bool dropped = false;
+    if (e < 0) {
+      report(a.status, 1, e_raw, (int)s);
+    } else {
+      const int64_t r = (int64_t)a.tile_base[(size_t)e * a.ntiles + tile] + s_cc[c * a.E + e] +
+                        __popc(m & ((1u << lane) - 1u));
+      dropped = a.capacity > 0 && r >= a.capacity;
+      if (!dropped) {
+        const int64_t q = (int64_t)a.offsets[e] + r;
+        if (q < 0 || q >= a.out_rows)
+          report(a.status, 2, (int)q, (int)s);
+        else
+          pos = (int)q;
+      }
+    }
+    a.inverse_perm[s] = pos;
+    if (a.drop_mask != nullptr) a.drop_mask[s] = dropped ? 1 : 0;
+  }
 }
 
 struct ScatterArgs {
@@ -189,40 +232,35 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
   }
 }
 
-int device_sms() {
-  static int cached[64] = {};
-  int dev = 0;
-  cudaGetDevice(&dev);
-  if (dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int sms = 148;
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    cached[dev] = sms;
-  }
-  return cached[dev];
-}
-
 }  // namespace
 
+int device_sms();
+
+size_t positions_smem(int K, int E) { return (size_t)((kTile * K + 31) / 32) * E * 2 + 16; }
+
+cudaError_t init_scatter_attributes() {
+  return cudaFuncSetAttribute(positions_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              (int)positions_smem(kMaxK, kMaxE));
+}
+
 cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                           const int32_t* ids, const int32_t* pair_rank, const int32_t* tile_base,
-                           int32_t* status, cudaStream_t s) {
+                           const int32_t* ids, const int32_t* tile_base, int32_t* status,
+                           cudaStream_t s) {
   if (p.T == 0) return cudaSuccess;
   PositionArgs pa;
   pa.ids = ids;
-  pa.pair_rank = pair_rank;
   pa.tile_base = tile_base;
   pa.offsets = b.offsets;
   pa.inverse_perm = b.inverse_perm;
   pa.drop_mask = b.drop_mask;
   pa.status = status;
-  pa.P = p.T * p.K;
+  pa.T = p.T;
   pa.capacity = p.capacity;
   pa.out_rows = p.out_rows;
   pa.E = p.E;
   pa.K = p.K;
   pa.ntiles = plan.ntiles;
-  positions_kernel<<<(unsigned)((pa.P + 255) / 256), 256, 0, s>>>(pa);
+  positions_kernel<<<(unsigned)plan.ntiles, kPosThreads, positions_smem(p.K, p.E), s>>>(pa);
   count_launch();
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;

@@ -46,7 +46,7 @@ def test_struct_layout_matches_header():
 
 def test_workspace_bytes_and_validation():
     n = _cabi.workspace_bytes(params())
-    assert n % 256 == 0 and n >= 1024 * 8 * 4 + 2 * 1024 * 2 * 4
+    assert n % 256 == 0 and n >= 1024 * 8 * 4 + 1024 * 2 * 4
     assert _cabi.workspace_bytes(params(T=0, out_rows=0)) >= 512
     bad = [dict(H=1001), dict(E=0), dict(E=257), dict(K=0), dict(K=9), dict(K=33, E=64),
            dict(n_groups=3), dict(E=64, K=8, n_groups=8, topk_groups=0, group_topk=2),
