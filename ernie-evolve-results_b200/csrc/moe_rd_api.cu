@@ -40,21 +40,14 @@ int make_plan(const moe_rd_params& p, Plan* plan) {
   if (gate == MOE_RD_GATE_GEMV && !gemv_eligible(p)) return MOE_RD_E_UNSUPPORTED;
   plan->gate = gate;
   plan->scatter = p.scatter_impl == MOE_RD_SCATTER_AUTO ? MOE_RD_SCATTER_SIMT : p.scatter_impl;
-  // One CTA per SM (148): split K by the power of two that fills the last wave
-  // best; ties go to the smaller split (less partial-sum traffic).
+  // Split K only when the token tiles alone cannot fill the SMs (148): every
+  // split writes and re-reads a [T,E] fp32 partial, which costs more than a
+  // ragged last wave once there is at least one full wave of tiles.
   int ksplit = 1;
   if (gate == MOE_RD_GATE_UMMA) {
     const int64_t mtiles = (p.T + 127) / 128;
     const int kblocks = p.H / 64;
-    double best = -1.0;
-    for (int s = 1; s <= 8 && kblocks / s >= 4; s *= 2) {
-      const int64_t ctas = mtiles * s;
-      const double util = (double)ctas / (double)(((ctas + 147) / 148) * 148);
-      if (util > best + 1e-9) {
-        best = util;
-        ksplit = s;
-      }
-    }
+    while (ksplit < 8 && mtiles * ksplit * 2 <= 148 && kblocks / (ksplit * 2) >= 4) ksplit *= 2;
   }
   plan->ksplit = ksplit;
   return MOE_RD_OK;
