@@ -18,7 +18,8 @@ GATE_IMPL = {"auto": 0, "simt": 1, "umma": 2, "external": 3, "gemv": 4}
 SCATTER_IMPL = {"auto": 0, "simt": 1, "bulk": 2}
 
 EXPORTS = (
-    "moe_rd_workspace_bytes", "moe_rd_route_dispatch", "moe_rd_route_dispatch_timed", "moe_rd_read_status",
+    "moe_rd_workspace_bytes", "moe_rd_route_dispatch", "moe_rd_route_dispatch_noalloc",
+    "moe_rd_route_dispatch_timed", "moe_rd_read_status",
     "moe_rd_launch_count", "moe_rd_strerror", "moe_rd_last_cuda_error", "moe_rd_version",
 )
 
@@ -64,6 +65,8 @@ def lib() -> ctypes.CDLL:
         L.moe_rd_route_dispatch.argtypes = [ctypes.POINTER(Params), ctypes.POINTER(Buffers),
                                             ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p]
         L.moe_rd_route_dispatch.restype = ctypes.c_int
+        L.moe_rd_route_dispatch_noalloc.argtypes = [ctypes.POINTER(Params), ctypes.POINTER(Buffers), ctypes.c_void_p]
+        L.moe_rd_route_dispatch_noalloc.restype = ctypes.c_int
         L.moe_rd_route_dispatch_timed.argtypes = [ctypes.POINTER(Params), ctypes.POINTER(Buffers),
                                                   ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p,
                                                   ctypes.POINTER(ctypes.c_float)]

@@ -117,6 +117,32 @@ int moe_rd_route_dispatch(const moe_rd_params* p, const moe_rd_buffers* b,
                           void* workspace, size_t workspace_bytes, void* stream);
 
 /*
+ * moe_rd_route_dispatch without a workspace argument, for callers that must
+ * not (or cannot) allocate device memory: a plug-in inside a host program that
+ * hands out every byte of device memory itself and treats a later cudaMalloc
+ * as an error, a service that froze its memory pool after start-up, or a bare
+ * C client with no allocator to carve a workspace from.  The scratch is a fixed
+ * array of MOE_RD_NOALLOC_MAX_BYTES inside the library's device image; every
+ * GPU that loads the library keeps that much reserved until the process exits.
+ * The caller still passes all inputs and outputs in `b`.
+ *
+ * - Problems whose moe_rd_workspace_bytes() exceeds MOE_RD_NOALLOC_MAX_BYTES are
+ *   refused with MOE_RD_E_TOO_LARGE before anything is launched.
+ * - The call itself makes no cudaMalloc/cudaFree and uses no allocating library.
+ * - The first call on each device looks up the array's device address (and, as
+ *   with moe_rd_route_dispatch, sets kernel attributes); make that first call
+ *   before starting any stream capture on that device.
+ * - All calls on a device share the one array.  Each call clears what it needs
+ *   zeroed, so calls that follow each other on a stream are fine, but two calls
+ *   whose kernels can overlap on the GPU (different streams, no ordering) race
+ *   on the scratch and corrupt each other.
+ * This entry point has no counterpart in the reference, whose run() allocates
+ * its arena with at::empty on every call (kernel.cu:4202-4268).
+ */
+#define MOE_RD_NOALLOC_MAX_BYTES (32u << 20)
+int moe_rd_route_dispatch_noalloc(const moe_rd_params* p, const moe_rd_buffers* b, void* stream);
+
+/*
  * Same work as moe_rd_route_dispatch, but with a CUDA event recorded on
  * `stream` between the stages; synchronises the stream and returns the device
  * time of each stage in milliseconds: stage_ms[0] gate product, [1] scoring /
