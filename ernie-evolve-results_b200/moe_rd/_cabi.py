@@ -19,7 +19,7 @@ SCATTER_IMPL = {"auto": 0, "simt": 1, "bulk": 2}
 
 EXPORTS = (
     "moe_rd_workspace_bytes", "moe_rd_route_dispatch", "moe_rd_route_dispatch_noalloc",
-    "moe_rd_route_dispatch_timed", "moe_rd_read_status",
+    "moe_rd_route_dispatch_timed", "moe_rd_read_status", "moe_rd_ep_unpack",
     "moe_rd_launch_count", "moe_rd_strerror", "moe_rd_last_cuda_error", "moe_rd_version",
 )
 
@@ -71,6 +71,10 @@ def lib() -> ctypes.CDLL:
                                                   ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p,
                                                   ctypes.POINTER(ctypes.c_float)]
         L.moe_rd_route_dispatch_timed.restype = ctypes.c_int
+        L.moe_rd_ep_unpack.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p,
+                                       ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
+                                       ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
+        L.moe_rd_ep_unpack.restype = ctypes.c_int
         L.moe_rd_read_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         L.moe_rd_read_status.restype = ctypes.c_int
         L.moe_rd_launch_count.argtypes = []

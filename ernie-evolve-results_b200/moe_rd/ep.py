@@ -1,0 +1,111 @@
+"""Expert-parallel dispatch across the GPUs of one box.
+
+Tokens shard by rank, experts shard by rank: rank d owns experts
+[d*E/W, (d+1)*E/W).  Every rank routes its own tokens against all E experts
+(``moe_rd.route_dispatch`` / ``Session.run``), which leaves its rows
+expert-major, i.e. destination-rank-major.  The exchange then is
+
+  1. counts first: an all-to-all of the kept rows per (destination, expert);
+  2. rows (and fp8 scales) by NCCL all-to-all with the split sizes from (1);
+  3. a local reorder from [source][expert] to [expert][source]
+     (``moe_rd_ep_unpack``), so that an expert's rows are contiguous and ordered
+     by (source rank, source slot order).
+
+The reference has no expert parallelism; the counts-then-rows shape follows its
+row-sharded embedding exchange (nanogpt-speedrun/track-1,
+track_1_short/sharded_rows.py:72-103; rows and scales as two exchanges,
+ngram_table.py:343-360).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import NamedTuple, Optional
+
+import torch
+import torch.distributed as dist
+
+from . import _cabi
+
+
+class EPResult(NamedTuple):
+    rows: torch.Tensor             # [capacity, H] expert-major; first offsets[-1] rows valid
+    scales: Optional[torch.Tensor]
+    offsets: torch.Tensor          # [E/W + 1] int32 (device)
+    counts: torch.Tensor           # [W, E/W] int32 (device): rows from source s for local expert le
+    recv_rows: int                 # rows received (host int)
+    sent_off_rank_bytes: int       # bytes this rank sent to other ranks
+
+
+def exchange_plan(kept: torch.Tensor, world: int, group=None):
+    """Counts first.  ``kept`` [E] = rows this rank dispatched per expert.
+    Returns (cnt [W, E/W] as received, send_splits, recv_splits) with the
+    splits as host lists.  Works on any backend (NCCL on device tensors, gloo
+    on CPU tensors); synchronises the host once to read the sizes."""
+    epr = kept.numel() // world
+    send = kept.reshape(world, epr).contiguous()
+    cnt = torch.empty_like(send)
+    dist.all_to_all_single(cnt, send, group=group)
+    sizes = torch.stack([send.sum(dim=1), cnt.sum(dim=1)]).cpu()
+    return cnt, [int(v) for v in sizes[0]], [int(v) for v in sizes[1]]
+
+
+def exchange_rows(rows: torch.Tensor, send_splits, recv_splits, out: torch.Tensor, group=None):
+    """Rows by all-to-all; ``out`` must hold sum(recv_splits) rows."""
+    n_send, n_recv = sum(send_splits), sum(recv_splits)
+    dist.all_to_all_single(out[:n_recv], rows[:n_send], recv_splits, send_splits, group=group)
+    return n_recv
+
+
+class ExpertParallel:
+    """Receive buffers are sized once for the worst case (every rank sends all of
+    its T*K rows here), so no allocation happens per exchange."""
+
+    def __init__(self, session, group=None, max_recv_rows: Optional[int] = None):
+        self.sess = session
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        E = session.E
+        if E % self.world:
+            raise ValueError("experts must divide evenly over the ranks")
+        self.epr = E // self.world
+        dev = session.device
+        send_rows = session.permuted.shape[0]
+        self.max_rows = int(max_recv_rows if max_recv_rows is not None else self.world * send_rows)
+        H = session.H
+        self.recv_rows = torch.empty((self.max_rows, H), dtype=session.permuted.dtype, device=dev)
+        self.out_rows = torch.empty_like(self.recv_rows)
+        if session.scales is not None:
+            nb = session.scales.shape[1]
+            self.recv_scales = torch.empty((self.max_rows, nb), dtype=torch.float32, device=dev)
+            self.out_scales = torch.empty_like(self.recv_scales)
+        else:
+            self.recv_scales = self.out_scales = None
+        self.local_offsets = torch.empty(self.epr + 1, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(8, dtype=torch.int32, device=dev)
+
+    def exchange(self, result=None) -> EPResult:
+        r = result if result is not None else self.sess.result()
+        offs = r.offsets
+        kept = offs[1:] - offs[:-1]
+        cnt, send_splits, recv_splits = exchange_plan(kept, self.world, self.group)
+        n_recv = sum(recv_splits)
+        if n_recv > self.max_rows:
+            raise RuntimeError(f"expert-parallel receive buffer too small: {n_recv} > {self.max_rows}")
+        exchange_rows(r.permuted, send_splits, recv_splits, self.recv_rows, self.group)
+        if r.scales is not None:
+            exchange_rows(r.scales, send_splits, recv_splits, self.recv_scales, self.group)
+        row_bytes = r.permuted.shape[1] * r.permuted.element_size()
+        dev = self.recv_rows.device
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+        def ptr(t):
+            return None if t is None else ctypes.c_void_p(t.data_ptr())
+        _cabi.check(_cabi.lib().moe_rd_ep_unpack(
+            ptr(cnt), self.world, self.epr, ptr(self.recv_rows), ptr(self.recv_scales if r.scales is not None else None),
+            ptr(self.out_rows), ptr(self.out_scales if r.scales is not None else None), ptr(self.local_offsets),
+            row_bytes, 0 if r.scales is None else r.scales.shape[1], self.max_rows, ptr(self.status), stream))
+        scale_bytes = 0 if r.scales is None else r.scales.shape[1] * 4
+        off_rank = (sum(send_splits) - send_splits[self.rank]) * (row_bytes + scale_bytes)
+        return EPResult(self.out_rows, self.out_scales if r.scales is not None else None, self.local_offsets, cnt,
+                        n_recv, off_rank)

@@ -143,6 +143,22 @@ int moe_rd_route_dispatch(const moe_rd_params* p, const moe_rd_buffers* b,
 int moe_rd_route_dispatch_noalloc(const moe_rd_params* p, const moe_rd_buffers* b, void* stream);
 
 /*
+ * Expert-parallel receive side.  After an all-to-all delivered, from every
+ * source rank s, that rank's rows for this rank's experts (rank-major:
+ * [s][local expert][rows], with cnt[s][le] rows each), reorder them into the
+ * expert-major buffer an expert GEMM consumes: [local expert][s][rows], and
+ * write local_offsets[experts_per_rank+1].  recv_scales/out_scales may both be
+ * NULL (bf16 rows).  `status` is an 8-word device block cleared by the caller;
+ * word 0 is set if the counts add up to more than max_rows.  The reference has
+ * no expert parallelism; its only counts-then-rows exchange is
+ * nanogpt-speedrun/track-1/track_1_short/sharded_rows.py:72-103.
+ */
+int moe_rd_ep_unpack(const int32_t* cnt, int world, int experts_per_rank, const void* recv_rows,
+                     const float* recv_scales, void* out_rows, float* out_scales,
+                     int32_t* local_offsets, int64_t row_bytes, int32_t scale_floats,
+                     int64_t max_rows, int32_t* status, void* stream);
+
+/*
  * Same work as moe_rd_route_dispatch, but with a CUDA event recorded on
  * `stream` between the stages; synchronises the stream and returns the device
  * time of each stage in milliseconds: stage_ms[0] gate product, [1] scoring /
