@@ -253,13 +253,18 @@ def run_ours(args, rank, world, local_rank):
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
-        # nvidia-smi needs a moment to start and samples every 100 ms: keep the same
-        # load running (untimed) until it has had time to see clocks under load.
-        t_hold = time.perf_counter()
-        while time.perf_counter() - t_hold < 1.5:
-            for _ in range(20):
-                step()
-            torch.cuda.synchronize()
+    # nvidia-smi needs a moment to start and samples every 100 ms: keep the same
+    # load running (untimed, on every rank alike) until it has seen clocks under load.
+    t_hold = time.perf_counter()
+    while True:
+        for _ in range(20):
+            step()
+        torch.cuda.synchronize()
+        more = torch.tensor([1 if time.perf_counter() - t_hold < 1.5 else 0], device=dev)
+        if world > 1:
+            dist.broadcast(more, src=0)
+        if int(more.item()) == 0:
+            break
     ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
     launches0 = _cabi.launch_count()
     barrier()
