@@ -3,11 +3,14 @@
 //
 // Replaces wsplit_kernel + the library router GEMM of the reference
 // (kernel.cu:1786-1824, 4327-4339) where the number of experts is small, and
-// serves every E as the order-defining product: lane l accumulates by fused
-// multiply-add, from 0, the elements h = 256*c + 8*l + j (c = 0,1,..; j = 0..7,
-// increasing), and the 32 lane sums are combined by the tree v[l] += v[l^off],
-// off = 16,8,4,2,1.  fp32 gate weights are read directly, so no hi/lo bf16
-// split (kernel.cu:1816-1822) is needed on this path.
+// serves every E as the order-defining product: lane l keeps two chains, one
+// for even and one for odd hidden indices; chain (l, p) accumulates by fused
+// multiply-add, from 0, the elements h = 256*c + 8*l + 2*m + p (c = 0,1,..;
+// m = 0..3, increasing); the lane's value is chain(l,0) + chain(l,1), and the 32
+// lane values are combined by the tree v[l] += v[l^off], off = 16,8,4,2,1.
+// (Two chains per lane are what the packed fma.rn.f32x2 of the fused GEMV
+// kernel computes from a bf16 pair.)  fp32 gate weights are read directly, so
+// no hi/lo bf16 split (kernel.cu:1816-1822) is needed on this path.
 #include "common.cuh"
 
 namespace moe_rd {
@@ -80,9 +83,9 @@ gate_simt_kernel(const uint16_t* __restrict__ x, const void* __restrict__ w,
   const int e0 = blockIdx.y * EB;
   if (t >= T) return;  // warp-uniform; the kernel has no block-level barrier
 
-  float acc[EB];
+  float acc[EB], acc1[EB];  // even-h chain, odd-h chain
 #pragma unroll
-  for (int e = 0; e < EB; ++e) acc[e] = 0.0f;
+  for (int e = 0; e < EB; ++e) acc[e] = acc1[e] = 0.0f;
 
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)t * H);
   const int nchunk = (H + 255) >> 8;
@@ -102,7 +105,12 @@ gate_simt_kernel(const uint16_t* __restrict__ x, const void* __restrict__ w,
           float wv[EB];
           load_w_row<EB, WD, VEC>(w, h0 + j, e0, E, wv);
 #pragma unroll
-          for (int e = 0; e < EB; ++e) acc[e] = fmaf(xf[j], wv[e], acc[e]);
+          for (int e = 0; e < EB; ++e) {
+            if (j & 1)
+              acc1[e] = fmaf(xf[j], wv[e], acc1[e]);
+            else
+              acc[e] = fmaf(xf[j], wv[e], acc[e]);
+          }
         }
       } else {
 #pragma unroll
@@ -111,13 +119,20 @@ gate_simt_kernel(const uint16_t* __restrict__ x, const void* __restrict__ w,
             float wv[8];
             load_w_col8<WD>(w, e0 + e, h0, H, wv);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) acc[e] = fmaf(xf[j], wv[j], acc[e]);
+            for (int j = 0; j < 8; ++j) {
+              if (j & 1)
+                acc1[e] = fmaf(xf[j], wv[j], acc1[e]);
+              else
+                acc[e] = fmaf(xf[j], wv[j], acc[e]);
+            }
           }
         }
       }
     }
   }
 
+#pragma unroll
+  for (int e = 0; e < EB; ++e) acc[e] = __fadd_rn(acc[e], acc1[e]);
 #pragma unroll
   for (int o = 16; o; o >>= 1) {
 #pragma unroll

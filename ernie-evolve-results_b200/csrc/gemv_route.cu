@@ -4,19 +4,24 @@
 //
 // Replaces wsplit_kernel + the router GEMM + topk_kernel of the reference
 // (kernel.cu:1786-1824, 4327-4339, 1829-1920) where the expert count is far
-// too small for a tensor-core tile.  The gate weight is staged once per block
-// in shared memory, in a lane-interleaved order that makes every 16-byte read
-// conflict-free; a warp carries 32/EB tokens at a time so each weight read
-// feeds several tokens, and the products accumulate with packed fma.rn.f32x2
-// (two IEEE fp32 FMAs per instruction).  The summation order per (token,
-// expert) is the fixed one of gate_simt.cu, so the logits are bit-identical
-// to that kernel's.
+// too small for a tensor-core tile.
+//
+// A lane owns hidden indices h = 256c + 8l + j.  Two consecutive bf16 of x
+// (h even, h odd) sit in one 32-bit word, and turning that word into a packed
+// pair of fp32 costs two integer operations.  The gate weight is staged once
+// per block in shared memory as fp32 in matching pairs {W[h_even][e],
+// W[h_odd][e]}, so one fma.rn.f32x2 advances the even-h chain and the odd-h
+// chain of one (token, expert) at once, with no conversion or duplication
+// inside the loop.  That is exactly the summation order gate_simt.cu defines
+// (32 lanes x 2 chains, then the tree), so the logits are bit-identical to that
+// kernel's.  A warp carries 32/EB tokens at a time so that every 16-byte weight
+// read feeds several tokens.
 #include "route_core.cuh"
 
 namespace moe_rd {
 namespace {
 
-constexpr int kGemvThreads = 256;
+constexpr int kGemvThreads = 512;
 constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kMaxDynSmem = 227 * 1024;
 
@@ -25,12 +30,9 @@ typedef unsigned long long u64;
 __device__ __forceinline__ void ffma2(u64& d, u64 a, u64 b) {
   asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(d) : "l"(a), "l"(b));
 }
-__device__ __forceinline__ u64 pack2(float lo, float hi) {
-  return (u64)__float_as_uint(lo) | ((u64)__float_as_uint(hi) << 32);
-}
 __device__ __forceinline__ float lo_of(u64 v) { return __uint_as_float((uint32_t)v); }
 __device__ __forceinline__ float hi_of(u64 v) { return __uint_as_float((uint32_t)(v >> 32)); }
-// two packed bf16 -> packed pair of fp32
+// two packed bf16 (even h in the low half) -> packed pair of fp32
 __device__ __forceinline__ u64 bf16x2_to_f32x2(uint32_t v) {
   return (u64)(v << 16) | ((u64)(v & 0xffff0000u) << 32);
 }
@@ -44,39 +46,58 @@ struct GemvArgs {
   int w_layout;
 };
 
-// Bytes of the staged weight: rows padded to whole 256-row chunks.
-__host__ __device__ inline size_t staged_w_bytes(int H, int EB, int wb) {
-  return (size_t)((H + 255) / 256) * 256 * EB * wb;
+// Bytes of the staged fp32 weight: rows padded to whole 256-row chunks.
+__host__ __device__ inline size_t staged_w_bytes(int H, int EB) {
+  return (size_t)((H + 255) / 256) * 256 * EB * 4;
+}
+
+// Shared-memory float index of W[h][e]: 16-byte unit (c, m, e/2) holds, for lane
+// l, {W[he][e0], W[ho][e0], W[he][e0+1], W[ho][e0+1]} with he = 256c + 8l + 2m.
+template <int EB>
+__device__ __forceinline__ int staged_index(int h, int e) {
+  const int c = h >> 8, l = (h >> 3) & 31, m = (h & 7) >> 1, p = h & 1;
+  return ((((c * 4 + m) * (EB / 2) + (e >> 1)) * 32 + l) << 2) + ((e & 1) << 1) + p;
 }
 
 template <int EB, int WD>
-__global__ void __launch_bounds__(kGemvThreads) gemv_route_kernel(const GemvArgs g,
-                                                                 const RouteArgs a) {
-  constexpr int WB = WD == MOE_RD_W_BF16 ? 2 : 4;  // bytes per weight
-  constexpr int U = EB * WB / 16;                  // 16-byte units per weight row
-  constexpr int TPW = 32 / EB;                     // tokens a warp carries at once
-  constexpr int NP = EB / 2;                       // accumulator pairs per token
-
+__global__ void __launch_bounds__(kGemvThreads, 1) gemv_route_kernel(const GemvArgs g,
+                                                                    const RouteArgs a) {
+  constexpr int TPW = 32 / EB;  // tokens a warp carries at once
   extern __shared__ __align__(16) unsigned char smem[];
-  uint4* s_w = reinterpret_cast<uint4*>(smem);
+  float* s_wf = reinterpret_cast<float*>(smem);
+  const uint4* s_w = reinterpret_cast<const uint4*>(smem);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nchunk = (g.H + 255) >> 8;
+  const int Hp = nchunk * 256;
 
-  // ---- stage the gate weight: element (h, e) of 16-byte unit u = e*WB/16 goes to
-  //      unit index ((c*8 + j)*U + u)*32 + l  with h = 256c + 8l + j.
-  if (g.w_layout == MOE_RD_W_LAYOUT_HE && a.E == EB) {
-    // A weight row is U whole 16-byte units, contiguous in memory: move units.
+  // ---- stage the gate weight (converted to fp32, zero padded) ----
+  if (g.w_layout == MOE_RD_W_LAYOUT_HE && a.E == EB && WD == MOE_RD_W_BF16) {
+    // a weight row is EB bf16 = EB/8 whole 16-byte vectors
     const uint4* w4 = static_cast<const uint4*>(g.w);
-    const int total = nchunk * 256 * U;
-    const int live = g.H * U;
-    for (int idx = tid; idx < total; idx += kGemvThreads) {
-      const int h = idx / U, u = idx - h * U;
-      const int c = h >> 8, l = (h >> 3) & 31, j = h & 7;
-      s_w[((c * 8 + j) * U + u) * 32 + l] = idx < live ? __ldg(w4 + idx) : make_uint4(0, 0, 0, 0);
+    constexpr int VPR = EB / 8;
+    for (int idx = tid; idx < Hp * VPR; idx += kGemvThreads) {
+      const int h = idx / VPR, q = idx - h * VPR;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (h < g.H) v = __ldg(w4 + idx);
+      float f[8];
+      unpack8(v, f);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s_wf[staged_index<EB>(h, q * 8 + i)] = f[i];
+    }
+  } else if (g.w_layout == MOE_RD_W_LAYOUT_HE && a.E == EB && WD == MOE_RD_W_F32) {
+    const float4* w4 = static_cast<const float4*>(g.w);
+    constexpr int VPR = EB / 4;
+    for (int idx = tid; idx < Hp * VPR; idx += kGemvThreads) {
+      const int h = idx / VPR, q = idx - h * VPR;
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (h < g.H) v = __ldg(w4 + idx);
+      s_wf[staged_index<EB>(h, q * 4 + 0)] = v.x;
+      s_wf[staged_index<EB>(h, q * 4 + 1)] = v.y;
+      s_wf[staged_index<EB>(h, q * 4 + 2)] = v.z;
+      s_wf[staged_index<EB>(h, q * 4 + 3)] = v.w;
     }
   } else {
-    const int Hp = nchunk * 256;
     const int total = Hp * EB;
     for (int idx = tid; idx < total; idx += kGemvThreads) {
       int h, e;
@@ -87,23 +108,22 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_route_kernel(const GemvArgs
         e = idx / Hp;
         h = idx - e * Hp;
       }
-      const bool live = h < g.H && e < a.E;
-      const size_t src = g.w_layout == MOE_RD_W_LAYOUT_HE ? (size_t)h * a.E + e : (size_t)e * g.H + h;
-      const int c = h >> 8, l = (h >> 3) & 31, j = h & 7;
-      const int byte = (((c * 8 + j) * U + (e * WB) / 16) * 32 + l) * 16 + (e * WB) % 16;
-      if (WD == MOE_RD_W_BF16)
-        *reinterpret_cast<uint16_t*>(smem + byte) =
-            live ? __ldg(static_cast<const uint16_t*>(g.w) + src) : (uint16_t)0;
-      else
-        *reinterpret_cast<float*>(smem + byte) =
-            live ? __ldg(static_cast<const float*>(g.w) + src) : 0.0f;
+      float v = 0.0f;
+      if (h < g.H && e < a.E) {
+        const size_t src =
+            g.w_layout == MOE_RD_W_LAYOUT_HE ? (size_t)h * a.E + e : (size_t)e * g.H + h;
+        v = WD == MOE_RD_W_BF16
+                ? __uint_as_float((uint32_t)__ldg(static_cast<const uint16_t*>(g.w) + src) << 16)
+                : __ldg(static_cast<const float*>(g.w) + src);
+      }
+      s_wf[staged_index<EB>(h, e)] = v;
     }
   }
   __syncthreads();
 
   // A unit = TPW consecutive tokens carried by one warp.  Block b owns the
-  // contiguous unit range [U*b/B, U*(b+1)/B), so with B a multiple of the SM
-  // count every SM gets the same work to within one unit.
+  // contiguous unit range [U*b/B, U*(b+1)/B), so with B = the SM count every SM
+  // gets the same work to within one unit.
   const int64_t units = (a.T + TPW - 1) / TPW;
   const int64_t ulo = units * blockIdx.x / gridDim.x;
   const int64_t uhi = units * (blockIdx.x + 1) / gridDim.x;
@@ -115,11 +135,11 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_route_kernel(const GemvArgs
       const int64_t t = min(tb + i, a.T - 1);  // clamp: rows past T are computed, not stored
       xr[i] = reinterpret_cast<const uint4*>(g.x + (size_t)t * g.H);
     }
-    u64 acc[TPW][NP];
+    u64 acc[TPW][EB];  // low half: even-h chain, high half: odd-h chain
 #pragma unroll
     for (int i = 0; i < TPW; ++i)
 #pragma unroll
-      for (int q = 0; q < NP; ++q) acc[i][q] = 0ull;
+      for (int e = 0; e < EB; ++e) acc[i][e] = 0ull;
 
     uint4 xn[TPW];
 #pragma unroll
@@ -138,50 +158,41 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_route_kernel(const GemvArgs
         for (int i = 0; i < TPW; ++i) xn[i] = __ldg(xr[i] + ((h0 + 256) >> 3));
       }
       if (h0 < g.H) {
-        const uint4* wrow = s_w + (size_t)c * 8 * U * 32 + lane;
+        const uint4* wc = s_w + (size_t)c * 4 * (EB / 2) * 32 + lane;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          u64 wp[NP];
-#pragma unroll
-          for (int u = 0; u < U; ++u) {
-            const uint4 v = wrow[(j * U + u) * 32];
-            if (WD == MOE_RD_W_BF16) {
-              wp[4 * u + 0] = bf16x2_to_f32x2(v.x);
-              wp[4 * u + 1] = bf16x2_to_f32x2(v.y);
-              wp[4 * u + 2] = bf16x2_to_f32x2(v.z);
-              wp[4 * u + 3] = bf16x2_to_f32x2(v.w);
-            } else {
-              wp[2 * u + 0] = (u64)v.x | ((u64)v.y << 32);
-              wp[2 * u + 1] = (u64)v.z | ((u64)v.w << 32);
-            }
-          }
+        for (int m = 0; m < 4; ++m) {
+          u64 xx[TPW];
 #pragma unroll
           for (int i = 0; i < TPW; ++i) {
-            const uint32_t pk = j < 2 ? xv[i].x : j < 4 ? xv[i].y : j < 6 ? xv[i].z : xv[i].w;
-            const float xf = (j & 1) ? bf16_hi(pk) : bf16_lo(pk);
-            const u64 xx = pack2(xf, xf);
+            const uint32_t pk = m == 0 ? xv[i].x : m == 1 ? xv[i].y : m == 2 ? xv[i].z : xv[i].w;
+            xx[i] = bf16x2_to_f32x2(pk);
+          }
 #pragma unroll
-            for (int q = 0; q < NP; ++q) ffma2(acc[i][q], xx, wp[q]);
+          for (int e2 = 0; e2 < EB / 2; ++e2) {
+            const uint4 v = wc[(m * (EB / 2) + e2) * 32];
+            const u64 w0 = (u64)v.x | ((u64)v.y << 32);
+            const u64 w1 = (u64)v.z | ((u64)v.w << 32);
+#pragma unroll
+            for (int i = 0; i < TPW; ++i) {
+              ffma2(acc[i][2 * e2], xx[i], w0);
+              ffma2(acc[i][2 * e2 + 1], xx[i], w1);
+            }
           }
         }
       }
     }
 
-    // lane sums -> token logits by the fixed tree; lane e keeps expert e, then
-    // the warp routes the token at once (E <= 32: one expert per lane)
+    // lane value = even chain + odd chain; lanes are summed by the fixed tree;
+    // lane e keeps expert e, and the warp routes the token at once
 #pragma unroll
     for (int i = 0; i < TPW; ++i) {
       float mine = 0.0f;
 #pragma unroll
-      for (int q = 0; q < NP; ++q) {
-        float v0 = lo_of(acc[i][q]), v1 = hi_of(acc[i][q]);
+      for (int e = 0; e < EB; ++e) {
+        float v = __fadd_rn(lo_of(acc[i][e]), hi_of(acc[i][e]));
 #pragma unroll
-        for (int o = 16; o; o >>= 1) {
-          v0 = __fadd_rn(v0, __shfl_xor_sync(kFull, v0, o));
-          v1 = __fadd_rn(v1, __shfl_xor_sync(kFull, v1, o));
-        }
-        if (lane == 2 * q) mine = v0;
-        if (lane == 2 * q + 1) mine = v1;
+        for (int o = 16; o; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(kFull, v, o));
+        if (lane == e) mine = v;
       }
       const int64_t t = tb + i;
       if (t < a.T) {  // warp-uniform
@@ -201,22 +212,15 @@ __global__ void __launch_bounds__(kGemvThreads) gemv_route_kernel(const GemvArgs
   }
 }
 
-size_t gemv_smem_bytes(const moe_rd_params& p, int EB) {
-  const int wb = p.w_dtype == MOE_RD_W_BF16 ? 2 : 4;
-  return staged_w_bytes(p.H, EB, wb);
-}
-
 int pick_eb(int E) { return E <= 8 ? 8 : E <= 16 ? 16 : 32; }
 
 template <int EB, int WD>
 cudaError_t launch_t(const moe_rd_params& p, const GemvArgs& g, const RouteArgs& a,
                      cudaStream_t s) {
-  const size_t smem = gemv_smem_bytes(p, EB);
-  // Two blocks per SM when shared memory allows (registers allow no more).
-  const int per_sm = smem * 2 + 2048 <= (size_t)kMaxDynSmem ? 2 : 1;
+  const size_t smem = staged_w_bytes(p.H, EB);
   const int64_t units = (p.T + 32 / EB - 1) / (32 / EB);
   const int64_t need = (units + kGemvWarps - 1) / kGemvWarps;
-  const int64_t cap = (int64_t)device_sms() * per_sm;
+  const int64_t cap = device_sms();  // one 512-thread block per SM (128 registers per thread)
   const int grid = (int)(need < cap ? need : cap);
   gemv_route_kernel<EB, WD><<<grid, kGemvThreads, smem, s>>>(g, a);
   count_launch();
@@ -227,7 +231,7 @@ cudaError_t launch_t(const moe_rd_params& p, const GemvArgs& g, const RouteArgs&
 
 bool gemv_eligible(const moe_rd_params& p) {
   if (p.E > 32 || p.T <= 0) return false;
-  return gemv_smem_bytes(p, pick_eb(p.E)) <= (size_t)kMaxDynSmem;
+  return staged_w_bytes(p.H, pick_eb(p.E)) <= (size_t)kMaxDynSmem;
 }
 
 cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
@@ -244,13 +248,10 @@ cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, c
   const int eb = pick_eb(p.E);
   const bool bf = p.w_dtype == MOE_RD_W_BF16;
   if (eb == 8)
-    return bf ? launch_t<8, MOE_RD_W_BF16>(p, g, a, s)
-              : launch_t<8, MOE_RD_W_F32>(p, g, a, s);
+    return bf ? launch_t<8, MOE_RD_W_BF16>(p, g, a, s) : launch_t<8, MOE_RD_W_F32>(p, g, a, s);
   if (eb == 16)
-    return bf ? launch_t<16, MOE_RD_W_BF16>(p, g, a, s)
-              : launch_t<16, MOE_RD_W_F32>(p, g, a, s);
-  return bf ? launch_t<32, MOE_RD_W_BF16>(p, g, a, s)
-            : launch_t<32, MOE_RD_W_F32>(p, g, a, s);
+    return bf ? launch_t<16, MOE_RD_W_BF16>(p, g, a, s) : launch_t<16, MOE_RD_W_F32>(p, g, a, s);
+  return bf ? launch_t<32, MOE_RD_W_BF16>(p, g, a, s) : launch_t<32, MOE_RD_W_F32>(p, g, a, s);
 }
 
 cudaError_t init_gemv_attributes() {

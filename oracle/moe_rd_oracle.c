@@ -38,10 +38,12 @@ static inline float bf16_to_f32(uint16_t b) {
  * The reference computes this product with a library GEMM whose summation
  * order is unspecified (kernel.cu:4327-4339) and recovers fp32-weight accuracy
  * by a hi/lo bf16 split (kernel.cu:1816-1822, 1849-1851).  Here the order is
- * fixed ("32x8 lane order"): partial l (0..31) accumulates, by fused
- * multiply-add from 0, the elements h = 256*c + 8*l + j for c = 0,1,.. and
- * j = 0..7 in increasing (c, j); the 32 partials are then summed by the
- * binary tree v[l] += v[l+off] for off = 16, 8, 4, 2, 1.
+ * fixed ("32 lanes x 2 chains"): chain (l, p), l = 0..31, p = 0..1,
+ * accumulates by fused multiply-add, from 0, the elements
+ * h = 256*c + 8*l + 2*m + p for c = 0,1,.. and m = 0..3 in increasing (c, m);
+ * lane l's value is chain(l,0) + chain(l,1); the 32 lane values are then summed
+ * by the binary tree v[l] += v[l+off] for off = 16, 8, 4, 2, 1.  (Two chains
+ * per lane are what a packed two-wide fp32 FMA over a bf16 pair computes.)
  *
  * w_dtype: 0 = fp32, 1 = bf16.  w_layout: 0 = [H,E] row-major, 1 = [E,H].
  * ---------------------------------------------------------------------- */
@@ -58,22 +60,28 @@ void moe_oracle_logits(const uint16_t* x, const void* w, int w_dtype,
   const int nchunk = (H + 255) / 256;
 #pragma omp parallel
   {
-    float* acc = (float*)malloc((size_t)32 * E * sizeof(float));
+    float* acc = (float*)malloc((size_t)64 * E * sizeof(float));
 #pragma omp for schedule(static)
     for (int64_t t = 0; t < T; ++t) {
-      memset(acc, 0, (size_t)32 * E * sizeof(float));
+      memset(acc, 0, (size_t)64 * E * sizeof(float));
       const uint16_t* xr = x + (size_t)t * H;
       for (int c = 0; c < nchunk; ++c)
         for (int l = 0; l < 32; ++l) {
           const int h0 = c * 256 + l * 8;
           if (h0 >= H) break;
-          float* a = acc + (size_t)l * E;
           for (int j = 0; j < 8; ++j) {
+            float* a = acc + ((size_t)l * 2 + (j & 1)) * E; /* chain (l, j&1) */
             const float xv = bf16_to_f32(xr[h0 + j]);
             const float* wr = wf + (size_t)(h0 + j) * E;
             for (int e = 0; e < E; ++e) a[e] = fmaf(xv, wr[e], a[e]);
           }
         }
+      for (int l = 0; l < 32; ++l) { /* lane value = even chain + odd chain, kept in slot l */
+        const float* a0 = acc + ((size_t)l * 2) * E;
+        const float* a1 = a0 + E;
+        float* d = acc + (size_t)l * E;
+        for (int e = 0; e < E; ++e) d[e] = a0[e] + a1[e];
+      }
       for (int off = 16; off; off >>= 1)
         for (int l = 0; l < off; ++l) {
           float* a = acc + (size_t)l * E;

@@ -63,29 +63,29 @@ def test_e4m3_matches_torch_cast_on_finite_range():
 
 
 def _logits_py(x_u16, w_f32, logit_bias=None):
-    """Independent restatement of the fixed summation order with float64
-    emulation of the fused multiply-add (products of a bf16 and an fp32 value
-    are exact in float64; the sum is rounded once to fp32)."""
+    """Independent restatement of the fixed summation order (32 lanes x 2
+    chains, then a tree) with float64 emulation of the fused multiply-add
+    (products of a bf16 and an fp32 value are exact in float64; the sum is
+    rounded once to fp32)."""
     T, H = x_u16.shape
     E = w_f32.shape[1]
     xf = bf16_to_f32_np(x_u16).astype(np.float64)
     wd = w_f32.astype(np.float64)
     z = np.zeros((T, E), np.float32)
     for t in range(T):
-        acc = np.zeros((32, E), np.float32)
+        acc = np.zeros((32, 2, E), np.float32)  # chain (lane, parity of h)
         for c in range((H + 255) // 256):
             for j in range(8):
                 hs = c * 256 + np.arange(32) * 8 + j
                 ok = hs < H
                 prod = xf[t, hs[ok]][:, None] * wd[hs[ok], :]
-                acc[ok] = (prod + acc[ok].astype(np.float64)).astype(np.float32)
+                acc[ok, j & 1] = (prod + acc[ok, j & 1].astype(np.float64)).astype(np.float32)
+        lane = acc[:, 0] + acc[:, 1]
         off = 16
         while off:
-            acc[:off] = acc[:off] + acc[off:2 * off]
+            lane[:off] = lane[:off] + lane[off:2 * off]
             off //= 2
-        z[t] = acc[0] + (logit_bias if logit_bias is not None else np.float32(0))
-        if logit_bias is None:
-            z[t] = acc[0]
+        z[t] = lane[0] + logit_bias if logit_bias is not None else lane[0]
     return z
 
 
