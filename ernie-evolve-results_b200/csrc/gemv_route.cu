@@ -32,9 +32,18 @@ __device__ __forceinline__ void ffma2(u64& d, u64 a, u64 b) {
 }
 __device__ __forceinline__ float lo_of(u64 v) { return __uint_as_float((uint32_t)v); }
 __device__ __forceinline__ float hi_of(u64 v) { return __uint_as_float((uint32_t)(v >> 32)); }
-// two packed bf16 (even h in the low half) -> packed pair of fp32
+// two packed bf16 (even h in the low half) -> packed pair of fp32.  The halves
+// are produced straight into the two registers of the 64-bit pair; building the
+// pair with 64-bit integer shifts and ors costs extra moves.
 __device__ __forceinline__ u64 bf16x2_to_f32x2(uint32_t v) {
-  return (u64)(v << 16) | ((u64)(v & 0xffff0000u) << 32);
+  u64 r;
+  asm("{\n\t.reg .b32 lo, hi;\n\t"
+      "shl.b32 lo, %1, 16;\n\t"
+      "and.b32 hi, %1, 0xffff0000;\n\t"
+      "mov.b64 %0, {lo, hi};\n\t}"
+      : "=l"(r)
+      : "r"(v));
+  return r;
 }
 
 struct GemvArgs {
@@ -65,7 +74,8 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_route_kernel(const GemvA
   constexpr int TPW = 32 / EB;  // tokens a warp carries at once
   extern __shared__ __align__(16) unsigned char smem[];
   float* s_wf = reinterpret_cast<float*>(smem);
-  const uint4* s_w = reinterpret_cast<const uint4*>(smem);
+  // read back as two 64-bit halves: each half is already a {W[he], W[ho]} pair
+  const ulonglong2* s_w = reinterpret_cast<const ulonglong2*>(smem);
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nchunk = (g.H + 255) >> 8;
@@ -158,7 +168,7 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_route_kernel(const GemvA
         for (int i = 0; i < TPW; ++i) xn[i] = __ldg(xr[i] + ((h0 + 256) >> 3));
       }
       if (h0 < g.H) {
-        const uint4* wc = s_w + (size_t)c * 4 * (EB / 2) * 32 + lane;
+        const ulonglong2* wc = s_w + (size_t)c * 4 * (EB / 2) * 32 + lane;
 #pragma unroll
         for (int m = 0; m < 4; ++m) {
           u64 xx[TPW];
@@ -169,13 +179,11 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_route_kernel(const GemvA
           }
 #pragma unroll
           for (int e2 = 0; e2 < EB / 2; ++e2) {
-            const uint4 v = wc[(m * (EB / 2) + e2) * 32];
-            const u64 w0 = (u64)v.x | ((u64)v.y << 32);
-            const u64 w1 = (u64)v.z | ((u64)v.w << 32);
+            const ulonglong2 v = wc[(m * (EB / 2) + e2) * 32];
 #pragma unroll
             for (int i = 0; i < TPW; ++i) {
-              ffma2(acc[i][2 * e2], xx[i], w0);
-              ffma2(acc[i][2 * e2 + 1], xx[i], w1);
+              ffma2(acc[i][2 * e2], xx[i], v.x);
+              ffma2(acc[i][2 * e2 + 1], xx[i], v.y);
             }
           }
         }
