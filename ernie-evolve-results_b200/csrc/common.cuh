@@ -8,6 +8,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <utility>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -27,8 +28,8 @@ struct Workspace {
   size_t ticket;       // int32[8]  scan ticket counter            } memset at the
   size_t tile_base;    // int32[E*ntiles] per-tile counts, scanned } start of a call
                        //           in place to bases
+  size_t counts;       // int32[E]  pairs per expert before dropping }
   size_t zero_bytes;   // length of that cleared prefix
-  size_t counts;       // int32[E]  pairs per expert before dropping
   size_t logits;       // float[T*E] when the caller passes no router_logits
   size_t ids;          // int32[T*K] when the caller passes no expert_ids
   size_t wt;           // bf16[E*H]  gate weight in [E,H] order for the tensor-core gate
@@ -53,13 +54,15 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
                              void* wt, float* partial, float* logits, int32_t* status,
                              cudaStream_t s);
 cudaError_t launch_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                         const float* logits, int32_t* ids, int32_t* tile_base, cudaStream_t s);
+                         const float* logits, int32_t* ids, int32_t* tile_base, int32_t* counts,
+                         cudaStream_t s);
 cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                                 const float* partial, int nsplit, const float* logit_bias,
                                 float* logits_out, int32_t* ids, int32_t* tile_base,
-                                cudaStream_t s);
+                                int32_t* counts, cudaStream_t s);
 cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                              float* logits_out, int32_t* ids, int32_t* tile_base, cudaStream_t s);
+                              float* logits_out, int32_t* ids, int32_t* tile_base, int32_t* counts,
+                              cudaStream_t s);
 cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                         int32_t* tile_base, int32_t* counts, int32_t* ticket, cudaStream_t s);
 cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
@@ -73,6 +76,34 @@ void count_launch(int n = 1);
 // device helpers
 // ---------------------------------------------------------------------------
 #ifdef __CUDACC__
+
+// Programmatic dependent launch.  Every kernel of the pipeline lets the next
+// launch start early (its blocks then park in pdl_sync until this grid has
+// completed and its writes are visible) and itself waits for the previous grid
+// before it touches global memory.  This hides the launch latency between the
+// five short kernels of a call.  Without the launch attribute both
+// instructions do nothing.
+__device__ __forceinline__ void pdl_sync() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+// <<<grid, block, smem, stream>>> with the programmatic-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // First failing check wins; later ones are dropped.  The caller skips the access.
 __device__ __forceinline__ void report(int32_t* status, int id, int a, int b) {

@@ -72,8 +72,11 @@ template <int EB, int WD>
 __global__ void __launch_bounds__(kGemvThreads, 1) gemv_route_kernel(const GemvArgs g,
                                                                     const RouteArgs a) {
   constexpr int TPW = 32 / EB;  // tokens a warp carries at once
+  pdl_sync();
   extern __shared__ __align__(16) unsigned char smem[];
   float* s_wf = reinterpret_cast<float*>(smem);
+  int* s_cnt = reinterpret_cast<int*>(smem + staged_w_bytes(g.H, EB));  // [32] block histogram
+  if (threadIdx.x < 32) s_cnt[threadIdx.x] = 0;
   // read back as two 64-bit halves: each half is already a {W[he], W[ho]} pair
   const ulonglong2* s_w = reinterpret_cast<const ulonglong2*>(smem);
 
@@ -214,10 +217,12 @@ __global__ void __launch_bounds__(kGemvThreads, 1) gemv_route_kernel(const GemvA
         int mysel;
         float myw;
         route_token<1>(a, z, lane, mysel, myw);
-        publish_token(a, t, lane, mysel, myw);
+        publish_token(a, t, lane, mysel, myw, s_cnt);
       }
     }
   }
+  __syncthreads();
+  flush_counts(a, s_cnt, kGemvThreads);
 }
 
 int pick_eb(int E) { return E <= 8 ? 8 : E <= 16 ? 16 : 32; }
@@ -225,25 +230,27 @@ int pick_eb(int E) { return E <= 8 ? 8 : E <= 16 ? 16 : 32; }
 template <int EB, int WD>
 cudaError_t launch_t(const moe_rd_params& p, const GemvArgs& g, const RouteArgs& a,
                      cudaStream_t s) {
-  const size_t smem = staged_w_bytes(p.H, EB);
+  const size_t smem = staged_w_bytes(p.H, EB) + 128;
   const int64_t units = (p.T + 32 / EB - 1) / (32 / EB);
   const int64_t need = (units + kGemvWarps - 1) / kGemvWarps;
   const int64_t cap = device_sms();  // one 512-thread block per SM (128 registers per thread)
   const int grid = (int)(need < cap ? need : cap);
-  gemv_route_kernel<EB, WD><<<grid, kGemvThreads, smem, s>>>(g, a);
+  const cudaError_t e =
+      launch_pdl(gemv_route_kernel<EB, WD>, dim3((unsigned)grid), dim3(kGemvThreads), smem, s, g, a);
   count_launch();
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace
 
 bool gemv_eligible(const moe_rd_params& p) {
   if (p.E > 32 || p.T <= 0) return false;
-  return staged_w_bytes(p.H, pick_eb(p.E)) <= (size_t)kMaxDynSmem;
+  return staged_w_bytes(p.H, pick_eb(p.E)) + 128 <= (size_t)kMaxDynSmem;
 }
 
 cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                              float* logits_out, int32_t* ids, int32_t* tile_base, cudaStream_t s) {
+                              float* logits_out, int32_t* ids, int32_t* tile_base, int32_t* counts,
+                              cudaStream_t s) {
   GemvArgs g;
   g.x = static_cast<const uint16_t*>(b.x);
   g.w = b.gate_w;
@@ -252,7 +259,7 @@ cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, c
   g.H = p.H;
   g.w_layout = p.w_layout;
   RouteArgs a;
-  fill_route_args(p, b, plan, nullptr, ids, tile_base, &a);
+  fill_route_args(p, b, plan, nullptr, ids, tile_base, counts, &a);
   const int eb = pick_eb(p.E);
   const bool bf = p.w_dtype == MOE_RD_W_BF16;
   if (eb == 8)

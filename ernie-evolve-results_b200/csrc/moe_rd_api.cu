@@ -59,8 +59,8 @@ void carve(const moe_rd_params& p, const Plan& plan, bool need_logits, bool need
   w->status = o; o += 256;
   w->ticket = o; o += 256;
   w->tile_base = o; o += up256((size_t)p.E * plan.ntiles * 4);
-  w->zero_bytes = o;
   w->counts = o; o += up256((size_t)p.E * 4);
+  w->zero_bytes = o;
   w->logits = o; if (need_logits) o += up256((size_t)p.T * p.E * 4);
   w->ids = o; if (need_ids) o += up256((size_t)p.T * p.K * 4);
   w->wt = o;
@@ -232,13 +232,13 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[1], s));
   if (p->T > 0) {
     if (plan.gate == MOE_RD_GATE_GEMV)
-      MOE_RD_CUDA(launch_gemv_route(*p, *b, plan, b->router_logits, ids, tile_base, s));
+      MOE_RD_CUDA(launch_gemv_route(*p, *b, plan, b->router_logits, ids, tile_base, counts, s));
     else if (plan.gate == MOE_RD_GATE_UMMA)
       MOE_RD_CUDA(launch_route_splits(*p, *b, plan, reinterpret_cast<float*>(ws + w.partial),
                                       plan.ksplit, b->logit_bias, b->router_logits, ids, tile_base,
-                                      s));
+                                      counts, s));
     else
-      MOE_RD_CUDA(launch_route(*p, *b, plan, logits, ids, tile_base, s));
+      MOE_RD_CUDA(launch_route(*p, *b, plan, logits, ids, tile_base, counts, s));
   }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[2], s));
   MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, ticket, s));

@@ -15,6 +15,10 @@ constexpr int kRouteWarps = kRouteThreads / 32;
 // number of tokens to within one, whatever T is.
 template <int EPL>
 __global__ void __launch_bounds__(kRouteThreads) route_kernel(const RouteArgs a) {
+  __shared__ int s_cnt[kMaxE];
+  for (int e = threadIdx.x; e < a.E; e += kRouteThreads) s_cnt[e] = 0;
+  __syncthreads();
+  pdl_sync();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t lo = a.T * blockIdx.x / gridDim.x;
   const int64_t hi = a.T * (blockIdx.x + 1) / gridDim.x;
@@ -37,16 +41,20 @@ __global__ void __launch_bounds__(kRouteThreads) route_kernel(const RouteArgs a)
     int mysel;
     float myw;
     route_token<EPL>(a, z, lane, mysel, myw);
-    publish_token(a, t, lane, mysel, myw);
+    publish_token(a, t, lane, mysel, myw, s_cnt);
   }
+  __syncthreads();
+  flush_counts(a, s_cnt, kRouteThreads);
 }
 
 // ---------------------------------------------------------------------------
-// Exclusive scan of the per-tile counts of one expert per block, then (in the
-// block that finishes last) the scan across experts with the capacity clamp.
-// Replaces the scan part of offsets_kernel (kernel.cu:2074-2086); offsets is
-// stored as E+1 exclusive starts instead of the reference's inclusive ends
-// `offs` plus exclusive starts `cursor`.
+// One block per expert: exclusive scan of that expert's per-tile counts (in
+// place, -> tile bases) and the expert's first row, offsets[e] = sum over the
+// experts before it of min(count, capacity).  The routing kernels already
+// accumulated counts[E], so no block waits for another.  Replaces the scan part
+// of offsets_kernel (kernel.cu:2074-2086); offsets is stored as E+1 exclusive
+// starts instead of the reference's inclusive ends `offs` plus exclusive starts
+// `cursor`.
 // ---------------------------------------------------------------------------
 constexpr int kScanThreads = 256;
 
@@ -75,12 +83,22 @@ __device__ __forceinline__ int block_exclusive_scan(int v, int* s_w, int& total)
 }
 
 __global__ void __launch_bounds__(kScanThreads)
-scan_kernel(int32_t* __restrict__ tile_base, int32_t* __restrict__ counts,
-            int32_t* __restrict__ user_counts, int32_t* __restrict__ offsets,
-            int32_t* __restrict__ ticket, int E, int ntiles, int64_t capacity) {
+scan_kernel(int32_t* __restrict__ tile_base, const int32_t* __restrict__ counts,
+            int32_t* __restrict__ user_counts, int32_t* __restrict__ offsets, int E, int ntiles,
+            int64_t capacity) {
   __shared__ int s_w[kScanThreads / 32];
-  __shared__ int s_last;
+  pdl_sync();
   const int e = blockIdx.x, tid = threadIdx.x;
+  // rows kept by the experts before this one (and by this one, for offsets[E])
+  int before = 0, mine = 0;
+  for (int i = tid; i <= e; i += kScanThreads) {
+    int v = counts[i];
+    if (i == e) {
+      if (user_counts != nullptr) user_counts[e] = v;
+    }
+    if (capacity > 0 && (int64_t)v > capacity) v = (int)capacity;
+    if (i < e) before += v; else mine = v;
+  }
   int32_t* col = tile_base + (size_t)e * ntiles;
   int carry = 0;
   for (int base = 0; base < ntiles; base += kScanThreads) {
@@ -91,31 +109,12 @@ scan_kernel(int32_t* __restrict__ tile_base, int32_t* __restrict__ counts,
     if (i < ntiles) col[i] = carry + ex;
     carry += total;
   }
+  int total_before, total_mine;
+  block_exclusive_scan(before, s_w, total_before);
+  block_exclusive_scan(mine, s_w, total_mine);
   if (tid == 0) {
-    counts[e] = carry;
-    if (user_counts != nullptr) user_counts[e] = carry;
-    __threadfence();
-    s_last = atomicAdd(ticket, 1) == E - 1;
-  }
-  __syncthreads();
-  if (!s_last) return;
-  __threadfence();
-  int run = 0;
-  for (int base = 0; base < E; base += kScanThreads) {
-    const int i = base + tid;
-    int v = 0;
-    if (i < E) {
-      v = __ldcg(counts + i);
-      if (capacity > 0 && (int64_t)v > capacity) v = (int)capacity;
-    }
-    int total;
-    const int ex = block_exclusive_scan(v, s_w, total);
-    if (i < E) offsets[i] = run + ex;
-    run += total;
-  }
-  if (tid == 0) {
-    offsets[E] = run;
-    *ticket = 0;
+    offsets[e] = total_before;
+    if (e == E - 1) offsets[E] = total_before + total_mine;
   }
 }
 
@@ -135,7 +134,8 @@ int device_sms() {
 }
 
 void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                     const float* logits, int32_t* ids, int32_t* tile_base, RouteArgs* a) {
+                     const float* logits, int32_t* ids, int32_t* tile_base, int32_t* counts,
+                     RouteArgs* a) {
   a->logits = logits;
   a->logit_bias = nullptr;
   a->logits_out = nullptr;
@@ -144,6 +144,7 @@ void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan
   a->ids = ids;
   a->weights = b.combine_weights;
   a->tile_counts = tile_base;
+  a->counts = counts;
   a->T = p.T;
   a->E = p.E;
   a->K = p.K;
@@ -159,16 +160,17 @@ void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan
 }
 
 cudaError_t launch_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                         const float* logits, int32_t* ids, int32_t* tile_base, cudaStream_t s) {
-  return launch_route_splits(p, b, plan, logits, 1, nullptr, nullptr, ids, tile_base, s);
+                         const float* logits, int32_t* ids, int32_t* tile_base, int32_t* counts,
+                         cudaStream_t s) {
+  return launch_route_splits(p, b, plan, logits, 1, nullptr, nullptr, ids, tile_base, counts, s);
 }
 
 cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                                 const float* partial, int nsplit, const float* logit_bias,
                                 float* logits_out, int32_t* ids, int32_t* tile_base,
-                                cudaStream_t s) {
+                                int32_t* counts, cudaStream_t s) {
   RouteArgs a;
-  fill_route_args(p, b, plan, partial, ids, tile_base, &a);
+  fill_route_args(p, b, plan, partial, ids, tile_base, counts, &a);
   a.nsplit = nsplit;
   a.logit_bias = logit_bias;
   a.logits_out = logits_out;
@@ -177,24 +179,27 @@ cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b,
   const int64_t need = (p.T + kRouteWarps - 1) / kRouteWarps;
   if (nblk > need) nblk = need;
   const dim3 grid((unsigned)nblk);
+  cudaError_t e;
   if (p.E <= 32)
-    route_kernel<1><<<grid, kRouteThreads, 0, s>>>(a);
+    e = launch_pdl(route_kernel<1>, grid, dim3(kRouteThreads), 0, s, a);
   else if (p.E <= 64)
-    route_kernel<2><<<grid, kRouteThreads, 0, s>>>(a);
+    e = launch_pdl(route_kernel<2>, grid, dim3(kRouteThreads), 0, s, a);
   else if (p.E <= 128)
-    route_kernel<4><<<grid, kRouteThreads, 0, s>>>(a);
+    e = launch_pdl(route_kernel<4>, grid, dim3(kRouteThreads), 0, s, a);
   else
-    route_kernel<8><<<grid, kRouteThreads, 0, s>>>(a);
+    e = launch_pdl(route_kernel<8>, grid, dim3(kRouteThreads), 0, s, a);
   count_launch();
-  return cudaGetLastError();
+  return e;
 }
 
 cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                         int32_t* tile_base, int32_t* counts, int32_t* ticket, cudaStream_t s) {
-  scan_kernel<<<(unsigned)p.E, kScanThreads, 0, s>>>(tile_base, counts, b.counts, b.offsets, ticket,
-                                                     p.E, plan.ntiles, p.capacity);
+  (void)ticket;
+  const cudaError_t e = launch_pdl(scan_kernel, dim3((unsigned)p.E), dim3(kScanThreads), 0, s,
+                                   tile_base, (const int32_t*)counts, b.counts, b.offsets, p.E,
+                                   plan.ntiles, p.capacity);
   count_launch();
-  return cudaGetLastError();
+  return e;
 }
 
 cudaError_t init_route_attributes() { return cudaSuccess; }

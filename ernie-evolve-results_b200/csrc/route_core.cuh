@@ -33,6 +33,7 @@ struct RouteArgs {
   int32_t* ids;              // [T,K]
   float* weights;            // [T,K]
   int32_t* tile_counts;      // [E][ntiles], zeroed before the kernel
+  int32_t* counts;           // [E], zeroed before the kernel
   int64_t T;
   int E, K, ntiles;
   int n_groups, topk_groups, group_topk;
@@ -211,20 +212,32 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)
   myw = __fmul_rn(wv, a.routed_scale);
 }
 
-// Lanes k < K publish slot k of token t: id, weight, and one count for the
-// (expert, tile) cell.
+// Lanes k < K publish slot k of token t: id, weight, one count for the
+// (expert, tile) cell, and one count in the block's shared histogram s_cnt[E]
+// (a popular expert would otherwise serialise tens of thousands of global
+// atomics on one address).
 __device__ __forceinline__ void publish_token(const RouteArgs& a, int64_t t, int lane, int mysel,
-                                              float myw) {
+                                              float myw, int* s_cnt) {
   if (lane < a.K) {
     const size_t s = (size_t)t * a.K + lane;
     a.ids[s] = mysel;
     a.weights[s] = myw;
     atomicAdd(a.tile_counts + (size_t)mysel * a.ntiles + (int)(t / kTile), 1);
+    atomicAdd(s_cnt + mysel, 1);
+  }
+}
+
+// Block-wide: add the shared histogram to counts[E].  Call after a barrier.
+__device__ __forceinline__ void flush_counts(const RouteArgs& a, const int* s_cnt, int nthreads) {
+  for (int e = threadIdx.x; e < a.E; e += nthreads) {
+    const int v = s_cnt[e];
+    if (v) atomicAdd(a.counts + e, v);
   }
 }
 
 void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                     const float* logits, int32_t* ids, int32_t* tile_base, RouteArgs* a);
+                     const float* logits, int32_t* ids, int32_t* tile_base, int32_t* counts,
+                     RouteArgs* a);
 int device_sms();
 
 }  // namespace moe_rd

@@ -50,6 +50,7 @@ constexpr int kPosThreads = 256;
 // the per-chunk counts are prefix-summed per expert in pair order.
 __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionArgs a) {
   extern __shared__ __align__(16) uint16_t s_cc[];  // [chunks][E]
+  pdl_sync();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int nwarps = kPosThreads / 32;
   const int tile = blockIdx.x;
@@ -162,6 +163,7 @@ struct UnitWalk {
 
 template <int FMT>
 __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterArgs a) {
+  pdl_sync();
   const int lane = threadIdx.x & 31;
   const int64_t w0 = (int64_t)blockIdx.x * kScatterWarps + (threadIdx.x >> 5);
   const int64_t W = (int64_t)gridDim.x * kScatterWarps;
@@ -260,9 +262,9 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   pa.E = p.E;
   pa.K = p.K;
   pa.ntiles = plan.ntiles;
-  positions_kernel<<<(unsigned)plan.ntiles, kPosThreads, positions_smem(p.K, p.E), s>>>(pa);
+  cudaError_t e = launch_pdl(positions_kernel, dim3((unsigned)plan.ntiles), dim3(kPosThreads),
+                             positions_smem(p.K, p.E), s, pa);
   count_launch();
-  cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return e;
 
   ScatterArgs a;
@@ -280,11 +282,11 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   const int64_t cap = (int64_t)device_sms() * 8;  // 8 resident blocks of 256 threads per SM
   const unsigned grid = (unsigned)(want < cap ? want : cap);
   if (fp8)
-    scatter_kernel<MOE_RD_ROWS_FP8_E4M3_B128><<<grid, kScatterThreads, 0, s>>>(a);
+    e = launch_pdl(scatter_kernel<MOE_RD_ROWS_FP8_E4M3_B128>, dim3(grid), dim3(kScatterThreads), 0, s, a);
   else
-    scatter_kernel<MOE_RD_ROWS_BF16><<<grid, kScatterThreads, 0, s>>>(a);
+    e = launch_pdl(scatter_kernel<MOE_RD_ROWS_BF16>, dim3(grid), dim3(kScatterThreads), 0, s, a);
   count_launch();
-  return cudaGetLastError();
+  return e;
 }
 
 }  // namespace moe_rd
