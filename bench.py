@@ -227,17 +227,19 @@ def run_ours(args, rank, world, local_rank):
     x = tensors["x"].to(dev)
     w = tensors["w"].to(dev)
     bias = None if tensors["bias"] is None else tensors["bias"].to(dev)
-    sess = Session(T, H, E, K, device=dev, w_dtype=w.dtype, **session_kwargs(kw))
+    fused = world > 1 and args.ep == "fused"
+    sess = Session(T, H, E, K, device=dev, w_dtype=w.dtype, scatter_impl="none" if fused else "auto",
+                   **session_kwargs(kw))
     ep = None
     if world > 1:
-        from moe_rd.ep import ExpertParallel
-        ep = ExpertParallel(sess, dist.group.WORLD)
+        from moe_rd.ep import ExpertParallel, ExpertParallelFused
+        ep = ExpertParallelFused(sess, dist.group.WORLD) if fused else ExpertParallel(sess, dist.group.WORLD)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def step():
         sess.run(x, w, bias)
         if ep is not None:
-            ep.exchange()
+            ep.exchange(x) if fused else ep.exchange()
 
     def barrier():
         if world > 1:
@@ -287,7 +289,6 @@ def run_ours(args, rank, world, local_rank):
     for _ in range(min(args.steps, 10)):
         flush.zero_()
         stage.append(sess.run_timed(x, w, bias))
-    clocks = sampler.stop() if rank == 0 else None
     stage_ms = [statistics.mean(s[i] for s in stage) for i in range(4)]
     kept = int(sess.offsets[-1].item())
     fp8 = kw.get("rows_format", "bf16") == "fp8"
@@ -295,17 +296,54 @@ def run_ours(args, rank, world, local_rank):
     scatter_bytes = T * H * 2 + kept * row_bytes + T * K * 4
     op_bytes = workloads.algorithmic_bytes(T, H, E, K, w_bytes=w.element_size(), fp8=fp8, kept_rows=kept)
     peak, peak_kind = measured_hbm_peak()
-    scatter_gbs = scatter_bytes / (stage_ms[3] * 1e-3) / 1e9
     op_ms = total_ms / args.steps
-    roofline = {
-        "bound": "hbm", "kernel": "scatter_kernel", "achieved": scatter_gbs, "peak": peak, "unit": "GB/s",
-        "frac": scatter_gbs / peak, "peak_kind": f"{peak_kind} HBM copy bandwidth", "traffic": None,
-        "bytes_per_launch": scatter_bytes, "kernel_ms": stage_ms[3],
-        "stage_ms": {"gate": stage_ms[0], "route": stage_ms[1], "scan": stage_ms[2], "scatter": stage_ms[3]},
-        "whole_op": {"algorithmic_bytes": op_bytes, "ms": op_ms, "achieved": op_bytes / (op_ms * 1e-3) / 1e9,
-                     "frac_of_measured": op_bytes / (op_ms * 1e-3) / 1e9 / peak,
-                     "frac_of_8000": op_bytes / (op_ms * 1e-3) / 1e9 / 8000.0},
-    }
+    whole = {"algorithmic_bytes": op_bytes, "ms": op_ms, "achieved": op_bytes / (op_ms * 1e-3) / 1e9,
+             "frac_of_measured": op_bytes / (op_ms * 1e-3) / 1e9 / peak,
+             "frac_of_8000": op_bytes / (op_ms * 1e-3) / 1e9 / 8000.0}
+    stages = {"gate": stage_ms[0], "route": stage_ms[1], "scan": stage_ms[2],
+              "positions_and_scatter": stage_ms[3]}
+    nvlink = None
+    if world > 1:
+        # the exchange alone, and the bytes that really left this GPU
+        evx = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(5)]
+        for s_, e_ in evx:
+            flush.zero_()
+            sess.run(x, w, bias)
+            s_.record()
+            ep.exchange(x) if fused else ep.exchange()
+            e_.record()
+        torch.cuda.synchronize()
+        ex_ms = statistics.mean(s_.elapsed_time(e_) for s_, e_ in evx)
+        offs = sess.offsets.cpu()
+        epr = E // world
+        egress = float((int(offs[E]) - int(offs[(rank + 1) * epr] - offs[rank * epr])) * row_bytes)
+        red = torch.tensor([ex_ms, egress, op_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(red, op=dist.ReduceOp.MAX)
+        ex_ms, egress, step_ms = (float(v) for v in red)
+        link_gbs = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool (900 nominal)
+        roof_ms = max(egress / link_gbs / 1e6, op_bytes / peak / 1e6)
+        nvlink = {"egress_bytes_per_rank_max": egress, "exchange_ms": ex_ms,
+                  "exchange_gbs": egress / (ex_ms * 1e-3) / 1e9, "link_peak_gbs": link_gbs,
+                  "link_peak_kind": "measured peer copy per direction (900 nominal)",
+                  "roofline_ms": roof_ms, "step_ms": step_ms, "frac_of_roofline": roof_ms / step_ms,
+                  "frac_of_900": max(egress / 900.0 / 1e6, op_bytes / peak / 1e6) / step_ms, "mode": args.ep}
+    clocks = sampler.stop() if rank == 0 else None
+    if fused:
+        roofline = {"bound": "nvlink", "kernel": "scatter_kernel<EP> (peer stores)",
+                    "achieved": nvlink["exchange_gbs"], "peak": nvlink["link_peak_gbs"], "unit": "GB/s",
+                    "frac": nvlink["exchange_gbs"] / nvlink["link_peak_gbs"],
+                    "peak_kind": nvlink["link_peak_kind"], "traffic": None,
+                    "bytes_per_launch": nvlink["egress_bytes_per_rank_max"], "kernel_ms": nvlink["exchange_ms"],
+                    "stage_ms": stages, "whole_op": whole}
+    else:
+        scatter_gbs = scatter_bytes / (stage_ms[3] * 1e-3) / 1e9
+        roofline = {
+            "bound": "hbm", "kernel": "scatter_kernel", "achieved": scatter_gbs, "peak": peak, "unit": "GB/s",
+            "frac": scatter_gbs / peak, "peak_kind": f"{peak_kind} HBM copy bandwidth", "traffic": None,
+            "bytes_per_launch": scatter_bytes, "kernel_ms": stage_ms[3],
+            "stage_ms": {"gate": stage_ms[0], "route": stage_ms[1], "scan": stage_ms[2], "scatter": stage_ms[3]},
+            "whole_op": whole,
+        }
 
     # --- end to end through the public callable with host buffers
     x_host = tensors["x"].pin_memory()
@@ -321,10 +359,16 @@ def run_ours(args, rank, world, local_rank):
 
     def e2e_step():
         x_in.copy_(x_host, non_blocking=True)
-        r = moe_rd.route_dispatch(x_in, w, bias, **kw)
-        if ep is not None:
-            ep.exchange(r)
-        src = [t for t in (r.permuted, r.scales, r.offsets, r.inverse_perm, r.combine_weights) if t is not None]
+        if fused:
+            r = moe_rd.route_dispatch(x_in, w, bias, scatter_impl="none", **kw)
+            o = ep.exchange(x_in, r)
+            src = [t for t in (o.rows, o.scales, r.offsets, r.inverse_perm, r.combine_weights) if t is not None]
+            src = [t[:h.shape[0]] if t.dim() == 2 and t.shape[0] > h.shape[0] else t for t, h in zip(src, host_out)]
+        else:
+            r = moe_rd.route_dispatch(x_in, w, bias, **kw)
+            if ep is not None:
+                ep.exchange(r)
+            src = [t for t in (r.permuted, r.scales, r.offsets, r.inverse_perm, r.combine_weights) if t is not None]
         for h, d in zip(host_out, src):
             h.copy_(d, non_blocking=True)
 
@@ -354,6 +398,7 @@ def run_ours(args, rank, world, local_rank):
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "steps": e2e_steps},
             "gpu_launches": int(launches),
+            "nvlink": nvlink,
             "clocks": clocks,
             "kept_rows": kept,
         }
@@ -373,6 +418,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--ep", default="fused", choices=["fused", "nccl"],
+                    help="expert-parallel exchange at N > 1: one peer-store kernel, or NCCL all-to-all + reorder")
     args = ap.parse_args()
     rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if world == 1 and args.gpus > 1:

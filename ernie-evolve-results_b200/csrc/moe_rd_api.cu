@@ -91,7 +91,7 @@ static int validate(const moe_rd_params* p) {
   if (p->rows_format != MOE_RD_ROWS_BF16 && p->rows_format != MOE_RD_ROWS_FP8_E4M3_B128)
     return MOE_RD_E_ENUM;
   if (p->gate_impl < MOE_RD_GATE_AUTO || p->gate_impl > MOE_RD_GATE_GEMV) return MOE_RD_E_ENUM;
-  if (p->scatter_impl < MOE_RD_SCATTER_AUTO || p->scatter_impl > MOE_RD_SCATTER_BULK)
+  if (p->scatter_impl < MOE_RD_SCATTER_AUTO || p->scatter_impl > MOE_RD_SCATTER_NONE)
     return MOE_RD_E_ENUM;
   if (p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128 && p->H % 128 != 0) return MOE_RD_E_SHAPE;
   if (p->capacity < 0 || p->out_rows < 0 || p->out_rows > 0x7fffffff) return MOE_RD_E_SHAPE;
@@ -186,13 +186,15 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   if (rc != MOE_RD_OK) return rc;
   if (plan.scatter == MOE_RD_SCATTER_BULK) return MOE_RD_E_UNSUPPORTED;
   if (b->offsets == nullptr) return MOE_RD_E_NULL;
-  if (p->T > 0 && (b->x == nullptr || b->permuted == nullptr || b->inverse_perm == nullptr ||
+  if (p->T > 0 && (b->x == nullptr || (b->permuted == nullptr && plan.scatter != MOE_RD_SCATTER_NONE) ||
+                   b->inverse_perm == nullptr ||
                    b->combine_weights == nullptr))
     return MOE_RD_E_NULL;
   if (plan.gate == MOE_RD_GATE_EXTERNAL ? (p->T > 0 && b->router_logits == nullptr)
                                         : (p->T > 0 && b->gate_w == nullptr))
     return MOE_RD_E_NULL;
-  if (p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128 && p->T > 0 && b->scales == nullptr)
+  if (p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128 && p->T > 0 && b->scales == nullptr &&
+      plan.scatter != MOE_RD_SCATTER_NONE)
     return MOE_RD_E_NULL;
   if (misaligned(b->x, 16) || misaligned(b->permuted, 16) || misaligned(b->gate_w, 16) ||
       misaligned(b->scales, 4))

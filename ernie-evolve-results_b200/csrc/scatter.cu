@@ -110,6 +110,8 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
   }
 }
 
+constexpr int kMaxWorld = 8;
+
 struct ScatterArgs {
   const uint16_t* x;
   const int32_t* inverse_perm;
@@ -117,7 +119,35 @@ struct ScatterArgs {
   float* scales;
   int64_t T;
   int H, K;
+  // expert-parallel destinations (EP == true): the row of pair (t,k) goes to
+  // peer_rows[e / epr] at row dest_base[e] + (inverse_perm - offsets[e])
+  const int32_t* ids;
+  const int32_t* offsets;
+  const int32_t* dest_base;
+  void* peer_rows[kMaxWorld];
+  float* peer_scales[kMaxWorld];
+  int epr;
 };
+
+// Destination of pair (t,k): local row index, or (peer buffer, row) when EP.
+template <bool EP>
+__device__ __forceinline__ bool resolve_dest(const ScatterArgs& a, int64_t t, int k, void*& rows,
+                                             float*& scales, int64_t& row) {
+  const int q = __ldg(a.inverse_perm + (size_t)t * a.K + k);
+  if (q < 0) return false;
+  if (!EP) {
+    rows = a.rows;
+    scales = a.scales;
+    row = q;
+    return true;
+  }
+  const int e = __ldg(a.ids + (size_t)t * a.K + k);
+  const int d = e / a.epr;
+  rows = a.peer_rows[d];
+  scales = a.peer_scales[d];
+  row = (int64_t)__ldg(a.dest_base + e) + (q - __ldg(a.offsets + e));
+  return true;
+}
 
 __device__ __forceinline__ uint32_t abs_bf16x2(uint32_t v) { return v & 0x7fff7fffu; }
 
@@ -161,7 +191,7 @@ struct UnitWalk {
   }
 };
 
-template <int FMT>
+template <int FMT, bool EP>
 __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterArgs a) {
   pdl_sync();
   const int lane = threadIdx.x & 31;
@@ -173,7 +203,6 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
     const int nvec = a.H >> 3;
     const int upr = (nvec + 127) >> 7;
     const uint4* x4 = reinterpret_cast<const uint4*>(a.x);
-    uint4* dst = reinterpret_cast<uint4*>(a.rows);
     UnitWalk wk(w0, W, upr);
     for (; wk.t < a.T; wk.next()) {
       const uint4* src = x4 + (size_t)wk.t * nvec;
@@ -182,11 +211,12 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
 #pragma unroll
       for (int u = 0; u < 4; ++u)
         if (vb + 32 * u < nvec) val[u] = __ldg(src + vb + 32 * u);
-      const int32_t* pos = a.inverse_perm + (size_t)wk.t * a.K;
       for (int k = 0; k < a.K; ++k) {
-        const int q = __ldg(pos + k);
-        if (q < 0) continue;
-        uint4* d = dst + (size_t)q * nvec;
+        void* rows;
+        float* scl;
+        int64_t q;
+        if (!resolve_dest<EP>(a, wk.t, k, rows, scl, q)) continue;
+        uint4* d = reinterpret_cast<uint4*>(rows) + (size_t)q * nvec;
 #pragma unroll
         for (int u = 0; u < 4; ++u)
           if (vb + 32 * u < nvec) __stcs(d + vb + 32 * u, val[u]);
@@ -199,7 +229,6 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
     const int nb = a.H >> 7;
     const int upr = (n16 + 31) >> 5;
     const uint4* x4 = reinterpret_cast<const uint4*>(a.x);
-    uint4* dst = reinterpret_cast<uint4*>(a.rows);
     UnitWalk wk(w0, W, upr);
     for (; wk.t < a.T; wk.next()) {
       const int v = wk.c * 32 + lane;
@@ -222,12 +251,13 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
       q.z = quant4(hi.x, hi.y, inv);
       q.w = quant4(hi.z, hi.w, inv);
       if (act) {
-        const int32_t* pos = a.inverse_perm + (size_t)wk.t * a.K;
         for (int k = 0; k < a.K; ++k) {
-          const int r = __ldg(pos + k);
-          if (r < 0) continue;
-          __stcs(dst + (size_t)r * n16 + v, q);
-          if ((lane & 7) == 0) a.scales[(size_t)r * nb + (v >> 3)] = scale;
+          void* rows;
+          float* scl;
+          int64_t r;
+          if (!resolve_dest<EP>(a, wk.t, k, rows, scl, r)) continue;
+          __stcs(reinterpret_cast<uint4*>(rows) + (size_t)r * n16 + v, q);
+          if ((lane & 7) == 0) scl[(size_t)r * nb + (v >> 3)] = scale;
         }
       }
     }
@@ -266,8 +296,9 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
                              positions_smem(p.K, p.E), s, pa);
   count_launch();
   if (e != cudaSuccess) return e;
+  if (plan.scatter == MOE_RD_SCATTER_NONE) return cudaSuccess;
 
-  ScatterArgs a;
+  ScatterArgs a = {};
   a.x = static_cast<const uint16_t*>(b.x);
   a.inverse_perm = b.inverse_perm;
   a.rows = b.permuted;
@@ -282,11 +313,118 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   const int64_t cap = (int64_t)device_sms() * 8;  // 8 resident blocks of 256 threads per SM
   const unsigned grid = (unsigned)(want < cap ? want : cap);
   if (fp8)
-    e = launch_pdl(scatter_kernel<MOE_RD_ROWS_FP8_E4M3_B128>, dim3(grid), dim3(kScatterThreads), 0, s, a);
+    e = launch_pdl(scatter_kernel<MOE_RD_ROWS_FP8_E4M3_B128, false>, dim3(grid), dim3(kScatterThreads), 0, s, a);
   else
-    e = launch_pdl(scatter_kernel<MOE_RD_ROWS_BF16>, dim3(grid), dim3(kScatterThreads), 0, s, a);
+    e = launch_pdl(scatter_kernel<MOE_RD_ROWS_BF16, false>, dim3(grid), dim3(kScatterThreads), 0, s, a);
   count_launch();
   return e;
 }
 
+namespace {
+
+// One block.  kept_all[s][e] = rows rank s dispatches to expert e.
+__global__ void __launch_bounds__(256)
+ep_plan_kernel(const int32_t* __restrict__ kept_all, int world, int rank, int E, int64_t max_rows,
+               int32_t* __restrict__ dest_base, int32_t* __restrict__ cnt,
+               int32_t* __restrict__ local_offsets, int32_t* __restrict__ status) {
+  __shared__ int s_tot[kMaxE];     // rows expert e receives from all ranks
+  __shared__ int s_before[kMaxE];  // rows expert e receives from ranks before `rank`
+  __shared__ int s_start[kMaxE];   // first row of expert e in its owner's buffer
+  const int epr = E / world;
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    int tot = 0, before = 0;
+    for (int s = 0; s < world; ++s) {
+      const int v = max(kept_all[(size_t)s * E + e], 0);
+      if (s < rank) before += v;
+      tot += v;
+    }
+    s_tot[e] = tot;
+    s_before[e] = before;
+  }
+  __syncthreads();
+  // exclusive prefix of s_tot inside every owner's expert range (<= 256 entries)
+  if (threadIdx.x < world) {
+    const int d = threadIdx.x;
+    int run = 0;
+    for (int le = 0; le < epr; ++le) {
+      s_start[d * epr + le] = run;
+      if (d == rank) local_offsets[le] = run;
+      run += s_tot[d * epr + le];
+    }
+    if (d == rank) {
+      local_offsets[epr] = run;
+      if ((int64_t)run > max_rows) report(status, 202, run, (int)max_rows);
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < E; e += blockDim.x) dest_base[e] = s_start[e] + s_before[e];
+  for (int i = threadIdx.x; i < world * epr; i += blockDim.x) {
+    const int s = i / epr, le = i - s * epr;
+    cnt[i] = max(kept_all[(size_t)s * E + rank * epr + le], 0);
+  }
+}
+
+}  // namespace
 }  // namespace moe_rd
+
+using namespace moe_rd;
+
+extern "C" int moe_rd_ep_plan(const int32_t* kept_all, int world, int rank, int E, int64_t max_rows,
+                              int32_t* dest_base, int32_t* cnt, int32_t* local_offsets,
+                              int32_t* status, void* stream) {
+  if (kept_all == nullptr || dest_base == nullptr || cnt == nullptr || local_offsets == nullptr ||
+      status == nullptr)
+    return MOE_RD_E_NULL;
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || E < 1 || E > kMaxE ||
+      E % world != 0 || max_rows < 0)
+    return MOE_RD_E_SHAPE;
+  ep_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      kept_all, world, rank, E, max_rows, dest_base, cnt, local_offsets, status);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
+}
+
+extern "C" int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const int32_t* expert_ids,
+                                 const int32_t* inverse_perm, const int32_t* offsets,
+                                 const int32_t* dest_base, int world, void* const* peer_rows,
+                                 float* const* peer_scales, void* stream) {
+  if (p == nullptr || x == nullptr || expert_ids == nullptr || inverse_perm == nullptr ||
+      offsets == nullptr || dest_base == nullptr || peer_rows == nullptr)
+    return MOE_RD_E_NULL;
+  if (world < 1 || world > kMaxWorld || p->E % world != 0 || p->T < 0 || p->H % 8 != 0)
+    return MOE_RD_E_SHAPE;
+  const bool fp8 = p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128;
+  if (fp8 && (peer_scales == nullptr || p->H % 128 != 0)) return MOE_RD_E_NULL;
+  if (p->T == 0) return MOE_RD_OK;
+  ScatterArgs a = {};
+  a.x = static_cast<const uint16_t*>(x);
+  a.inverse_perm = inverse_perm;
+  a.T = p->T;
+  a.H = p->H;
+  a.K = p->K;
+  a.ids = expert_ids;
+  a.offsets = offsets;
+  a.dest_base = dest_base;
+  a.epr = p->E / world;
+  for (int d = 0; d < world; ++d) {
+    if (peer_rows[d] == nullptr || (reinterpret_cast<uintptr_t>(peer_rows[d]) & 15))
+      return MOE_RD_E_ALIGN;
+    a.peer_rows[d] = peer_rows[d];
+    a.peer_scales[d] = fp8 ? peer_scales[d] : nullptr;
+    if (fp8 && a.peer_scales[d] == nullptr) return MOE_RD_E_NULL;
+  }
+  const int64_t upr = fp8 ? ((p->H >> 4) + 31) >> 5 : ((p->H >> 3) + 127) >> 7;
+  const int64_t units = p->T * upr;
+  const int64_t want = (units + kScatterWarps - 1) / kScatterWarps;
+  const int64_t cap = (int64_t)device_sms() * 8;
+  const unsigned grid = (unsigned)(want < cap ? want : cap);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (fp8)
+    e = launch_pdl(scatter_kernel<MOE_RD_ROWS_FP8_E4M3_B128, true>, dim3(grid),
+                   dim3(kScatterThreads), 0, s, a);
+  else
+    e = launch_pdl(scatter_kernel<MOE_RD_ROWS_BF16, true>, dim3(grid), dim3(kScatterThreads), 0, s, a);
+  count_launch();
+  return e == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
+}

@@ -88,9 +88,11 @@ def _impl(x, gate_weight, logit_bias, select_bias, given_logits, top_k, score_fn
     if capacity > 0:
         out_rows = min(out_rows, E * capacity)
     fp8 = rows_format == _cabi.ROWS_FORMAT["fp8"]
+    move_rows = scatter_impl != _cabi.SCATTER_IMPL["none"]
     with torch.cuda.device(dev):
-        permuted = torch.empty((out_rows, H), dtype=torch.uint8 if fp8 else torch.bfloat16, device=dev)
-        scales = torch.empty((out_rows, H // 128), dtype=torch.float32, device=dev) if fp8 else None
+        permuted = torch.empty((out_rows if move_rows else 0, H), dtype=torch.uint8 if fp8 else torch.bfloat16,
+                               device=dev)
+        scales = torch.empty((out_rows if move_rows else 0, H // 128), dtype=torch.float32, device=dev) if fp8 else None
         offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
         inv = torch.empty((T, K), dtype=torch.int32, device=dev)
         weights = torch.empty((T, K), dtype=torch.float32, device=dev)

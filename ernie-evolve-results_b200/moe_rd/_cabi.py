@@ -15,11 +15,12 @@ W_DTYPE = {"fp32": 0, "bf16": 1}
 W_LAYOUT = {"HE": 0, "EH": 1}
 ROWS_FORMAT = {"bf16": 0, "fp8": 1}
 GATE_IMPL = {"auto": 0, "simt": 1, "umma": 2, "external": 3, "gemv": 4}
-SCATTER_IMPL = {"auto": 0, "simt": 1, "bulk": 2}
+SCATTER_IMPL = {"auto": 0, "simt": 1, "bulk": 2, "none": 3}
 
 EXPORTS = (
     "moe_rd_workspace_bytes", "moe_rd_route_dispatch", "moe_rd_route_dispatch_noalloc",
-    "moe_rd_route_dispatch_timed", "moe_rd_read_status", "moe_rd_ep_unpack",
+    "moe_rd_route_dispatch_timed", "moe_rd_read_status", "moe_rd_ep_unpack", "moe_rd_ep_plan",
+    "moe_rd_ep_scatter",
     "moe_rd_launch_count", "moe_rd_strerror", "moe_rd_last_cuda_error", "moe_rd_version",
 )
 
@@ -75,6 +76,14 @@ def lib() -> ctypes.CDLL:
                                        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int64,
                                        ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
         L.moe_rd_ep_unpack.restype = ctypes.c_int
+        L.moe_rd_ep_plan.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64,
+                                     ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        L.moe_rd_ep_plan.restype = ctypes.c_int
+        L.moe_rd_ep_scatter.argtypes = [ctypes.POINTER(Params), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                        ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
+                                        ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
+                                        ctypes.c_void_p]
+        L.moe_rd_ep_scatter.restype = ctypes.c_int
         L.moe_rd_read_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         L.moe_rd_read_status.restype = ctypes.c_int
         L.moe_rd_launch_count.argtypes = []

@@ -109,3 +109,73 @@ class ExpertParallel:
         off_rank = (sum(send_splits) - send_splits[self.rank]) * (row_bytes + scale_bytes)
         return EPResult(self.out_rows, self.out_scales if r.scales is not None else None, self.local_offsets, cnt,
                         n_recv, off_rank)
+
+
+class ExpertParallelFused:
+    """Expert-parallel dispatch without a send buffer: after the counts are
+    gathered, ONE kernel reads each token row once and stores it straight into
+    the owner's expert-major buffer over NVLink (plain 16-byte peer stores, no
+    multicast), already at its final row, so there is no receive-side reorder.
+    Use a ``Session(..., scatter_impl="none")``.
+
+    The receive buffers live in symmetric memory (torch's intra-node peer
+    mapping) and are sized once for the worst case.  ``exchange`` synchronises
+    nothing on the host: gather of counts (NCCL), plan kernel, scatter kernel,
+    and a one-element all-reduce that orders every rank's stores before anyone
+    reads its buffer.
+    """
+
+    def __init__(self, session, group=None, max_recv_rows: Optional[int] = None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.sess = session
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        E, K, T, H = session.E, session.K, session.T, session.H
+        if E % self.world or self.world > 8:
+            raise ValueError("experts must divide evenly over at most 8 ranks")
+        self.epr = E // self.world
+        dev = session.device
+        self.fp8 = session.fp8
+        self.row_bytes = H * (1 if self.fp8 else 2)
+        self.nb = H // 128 if self.fp8 else 0
+        per_rank = T * K if not session.params.capacity else min(T * K, E * session.params.capacity)
+        self.max_rows = int(max_recv_rows if max_recv_rows is not None else self.world * per_rank)
+        rows_bytes = (self.max_rows * self.row_bytes + 255) // 256 * 256
+        total = rows_bytes + self.max_rows * self.nb * 4
+        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+        self.hdl = symm_mem.rendezvous(self.buf, self.group)
+        ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+        self.peer_rows = (ctypes.c_void_p * self.world)(*ptrs)
+        self.peer_scales = (ctypes.c_void_p * self.world)(*[p + rows_bytes for p in ptrs])
+        rows_u8 = self.buf[: self.max_rows * self.row_bytes]
+        self.rows = (rows_u8 if self.fp8 else rows_u8.view(torch.bfloat16)).view(self.max_rows, H)
+        self.scales = (self.buf[rows_bytes: rows_bytes + self.max_rows * self.nb * 4].view(torch.float32)
+                       .view(self.max_rows, self.nb)) if self.fp8 else None
+        self.kept_all = torch.empty((self.world, E), dtype=torch.int32, device=dev)
+        self.dest_base = torch.empty(E, dtype=torch.int32, device=dev)
+        self.cnt = torch.empty((self.world, self.epr), dtype=torch.int32, device=dev)
+        self.local_offsets = torch.empty(self.epr + 1, dtype=torch.int32, device=dev)
+        self.status = torch.zeros(8, dtype=torch.int32, device=dev)
+        self.token = torch.zeros(1, dtype=torch.int32, device=dev)
+
+    def exchange(self, x: torch.Tensor, result=None) -> EPResult:
+        r = result if result is not None else self.sess.result()
+        offs = r.offsets
+        kept = (offs[1:] - offs[:-1]).contiguous()
+        # also a barrier: nobody overwrites a buffer its owner may still be reading
+        dist.all_gather_into_tensor(self.kept_all, kept, group=self.group)
+        dev = self.buf.device
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+        def ptr(t):
+            return ctypes.c_void_p(t.data_ptr())
+        L = _cabi.lib()
+        _cabi.check(L.moe_rd_ep_plan(ptr(self.kept_all), self.world, self.rank, self.sess.E, self.max_rows,
+                                     ptr(self.dest_base), ptr(self.cnt), ptr(self.local_offsets), ptr(self.status),
+                                     stream))
+        _cabi.check(L.moe_rd_ep_scatter(ctypes.byref(self.sess.params), ptr(x), ptr(r.expert_ids),
+                                        ptr(r.inverse_perm), ptr(offs), ptr(self.dest_base), self.world,
+                                        self.peer_rows, self.peer_scales, stream))
+        dist.all_reduce(self.token, group=self.group)  # every rank's stores are done and visible after this
+        return EPResult(self.rows, self.scales, self.local_offsets, self.cnt, -1, -1)

@@ -29,8 +29,11 @@ class Session:
         self.fp8 = rows_format == "fp8"
         out_rows = T * K if not capacity else min(T * K, E * capacity)
         d = self.device
-        self.permuted = torch.empty((out_rows, H), dtype=torch.uint8 if self.fp8 else torch.bfloat16, device=d)
-        self.scales = torch.empty((out_rows, H // 128), dtype=torch.float32, device=d) if self.fp8 else None
+        self.rows_moved_here = scatter_impl != "none"  # "none": rows leave through moe_rd.ep instead
+        self.permuted = (torch.empty((out_rows, H), dtype=torch.uint8 if self.fp8 else torch.bfloat16, device=d)
+                         if self.rows_moved_here else None)
+        self.scales = (torch.empty((out_rows, H // 128), dtype=torch.float32, device=d)
+                       if self.fp8 and self.rows_moved_here else None)
         self.offsets = torch.empty(E + 1, dtype=torch.int32, device=d)
         self.inverse_perm = torch.empty((T, K), dtype=torch.int32, device=d)
         self.combine_weights = torch.empty((T, K), dtype=torch.float32, device=d)

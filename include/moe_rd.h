@@ -49,7 +49,13 @@ enum {
   MOE_RD_GATE_GEMV = 4      /* warp GEMV fused with scoring/top-k (E <= 32, weight fits in
                                shared memory); same logit bits as MOE_RD_GATE_SIMT */
 };
-enum { MOE_RD_SCATTER_AUTO = 0, MOE_RD_SCATTER_SIMT = 1, MOE_RD_SCATTER_BULK = 2 };
+enum {
+  MOE_RD_SCATTER_AUTO = 0,
+  MOE_RD_SCATTER_SIMT = 1,
+  MOE_RD_SCATTER_BULK = 2,
+  MOE_RD_SCATTER_NONE = 3 /* routing, offsets and inverse permutation only; rows are moved by
+                             moe_rd_ep_scatter (expert-parallel dispatch) */
+};
 
 /*
  * Problem description.  Replaces the compile-time constants NE/TOPK and the
@@ -157,6 +163,37 @@ int moe_rd_ep_unpack(const int32_t* cnt, int world, int experts_per_rank, const 
                      const float* recv_scales, void* out_rows, float* out_scales,
                      int32_t* local_offsets, int64_t row_bytes, int32_t scale_floats,
                      int64_t max_rows, int32_t* status, void* stream);
+
+/*
+ * Expert-parallel dispatch by direct peer stores (one kernel moves the rows and
+ * crosses NVLink; no send buffer, no receive-side reorder).  Rank `rank` of
+ * `world` owns experts [rank*E/world, (rank+1)*E/world).
+ *
+ * moe_rd_ep_plan: from kept_all[world][E] (rows every rank dispatches to every
+ * expert, gathered beforehand) computes, on this rank, dest_base[E] = the row in
+ * the owner's buffer where THIS rank's rows for expert e start (experts of an
+ * owner are contiguous, and inside an expert rows are ordered by source rank),
+ * cnt[world][E/world] = rows this rank receives per (source, local expert), and
+ * local_offsets[E/world + 1].  status word 0 is set if this rank would receive
+ * more than max_rows.
+ *
+ * moe_rd_ep_scatter: for every kept pair (t,k) of this rank, row
+ * dest_base[e] + (inverse_perm[t,k] - offsets[e]) of the owner's buffer
+ * peer_rows[e / (E/world)] receives the token row (bf16 copy or fp8 bytes plus
+ * scales into peer_scales[..]).  peer_rows/peer_scales are host arrays of
+ * `world` device pointers that this GPU can store to (peer-mapped memory; the
+ * entry for `rank` is local).  Plain 16-byte stores; no multicast.  The caller
+ * orders a cross-rank barrier after it before anyone reads the buffers.
+ * Run the local pipeline with MOE_RD_SCATTER_NONE first.  No counterpart in the
+ * reference (it has no expert parallelism).
+ */
+int moe_rd_ep_plan(const int32_t* kept_all, int world, int rank, int E, int64_t max_rows,
+                   int32_t* dest_base, int32_t* cnt, int32_t* local_offsets, int32_t* status,
+                   void* stream);
+int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const int32_t* expert_ids,
+                      const int32_t* inverse_perm, const int32_t* offsets,
+                      const int32_t* dest_base, int world, void* const* peer_rows,
+                      float* const* peer_scales, void* stream);
 
 /*
  * Same work as moe_rd_route_dispatch, but with a CUDA event recorded on

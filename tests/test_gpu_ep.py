@@ -23,7 +23,7 @@ def _free_port():
         return s.getsockname()[1]
 
 
-def _worker(rank, world, port, T0, H, q):
+def _worker(rank, world, port, T0, H, mode, q):
     try:
         sys.path[:0] = [str(ROOT), str(ROOT / "ernie-evolve-results_b200"), str(ROOT / "tests")]
         import torch.distributed as dist
@@ -34,19 +34,22 @@ def _worker(rank, world, port, T0, H, q):
                                 timeout=datetime.timedelta(seconds=120))
         from moe_rd import workloads
         from moe_rd.runtime import Session
-        from moe_rd.ep import ExpertParallel
+        from moe_rd.ep import ExpertParallel, ExpertParallelFused
         from oracle import cpu_oracle
         import _util
         E, K = 256, 8
         T = T0 + 64 * rank  # ragged: ranks hold different token counts
         t, kw = workloads.make("c5", T=T, H=H, rank=rank)
+        fused = mode == "fused"
         sess = Session(T, H, E, K, device=dev, score_fn="sigmoid", bias_mode="select", n_groups=8, topk_groups=4,
-                       group_topk=2, routed_scale=2.5, rows_format="fp8", return_logits=True)
-        ep = ExpertParallel(sess, max_recv_rows=world * (T0 + 64 * world) * K)
+                       group_topk=2, routed_scale=2.5, rows_format="fp8", return_logits=True,
+                       scatter_impl="none" if fused else "auto")
+        cls = ExpertParallelFused if fused else ExpertParallel
+        ep = cls(sess, max_recv_rows=world * (T0 + 64 * world) * K)
         x, w, b = t["x"].to(dev), t["w"].to(dev), t["bias"].to(dev)
         for _ in range(2):  # twice: buffers are reused
             sess.run(x, w, b)
-            out = ep.exchange()
+            out = ep.exchange(x) if fused else ep.exchange()
         torch.cuda.synchronize()
         sess.status()
         # every rank's GPU logits, so that the oracle can restate all ranks
@@ -59,7 +62,7 @@ def _worker(rank, world, port, T0, H, q):
             tr, kwr = workloads.make("c5", T=T0 + 64 * r, H=H, rank=r)
             per.append(_util.run_oracle(tr, kwr, given_logits=gathered[r]))
         ref = cpu_oracle.ep_exchange(per, E, world)[rank]
-        n = out.recv_rows
+        n = int(out.offsets[-1].item())
         assert n == ref["rows"].shape[0]
         np.testing.assert_array_equal(out.counts.cpu().numpy(), ref["counts"])
         np.testing.assert_array_equal(out.offsets.cpu().numpy(), ref["offsets"])
@@ -75,13 +78,14 @@ def _worker(rank, world, port, T0, H, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-def test_expert_parallel_exchange_matches_oracle():
+@pytest.mark.parametrize("mode", ["nccl", "fused"])
+def test_expert_parallel_exchange_matches_oracle(mode):
     import torch.multiprocessing as mp
     world = min(torch.cuda.device_count(), 4)
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_worker, args=(r, world, port, 300, 1024, q)) for r in range(world)]
+    procs = [ctx.Process(target=_worker, args=(r, world, port, 300, 1024, mode, q)) for r in range(world)]
     for p in procs:
         p.start()
     res = [q.get(timeout=600) for _ in procs]
