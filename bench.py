@@ -412,6 +412,9 @@ def run_ours(args, rank, world, local_rank):
 
 
 def main():
+    # NCCL prints its version banner on stdout at this level; stdout carries the one JSON line
+    if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
+        os.environ["NCCL_DEBUG"] = "WARN"
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
