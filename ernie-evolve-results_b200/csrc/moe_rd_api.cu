@@ -19,6 +19,8 @@ cudaError_t init_route_attributes();
 cudaError_t init_umma_attributes();
 cudaError_t init_gemv_attributes();
 cudaError_t init_scatter_attributes();
+cudaError_t init_bulk_attributes();
+bool bulk_scatter_eligible(const moe_rd_params& p);
 
 static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -120,6 +122,8 @@ static cudaError_t init_device_once() {
   if (e != cudaSuccess) return e;
   e = init_scatter_attributes();
   if (e != cudaSuccess) return e;
+  e = init_bulk_attributes();
+  if (e != cudaSuccess) return e;
   done[dev] = true;
   return cudaSuccess;
 }
@@ -184,7 +188,9 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   Plan plan;
   rc = make_plan(*p, &plan);
   if (rc != MOE_RD_OK) return rc;
-  if (plan.scatter == MOE_RD_SCATTER_BULK) return MOE_RD_E_UNSUPPORTED;
+  if (plan.scatter == MOE_RD_SCATTER_BULK &&
+      (!bulk_scatter_eligible(*p) || misaligned(b->scales, 16) || misaligned(b->permuted, 16)))
+    return MOE_RD_E_UNSUPPORTED;
   if (b->offsets == nullptr) return MOE_RD_E_NULL;
   if (p->T > 0 && (b->x == nullptr || (b->permuted == nullptr && plan.scatter != MOE_RD_SCATTER_NONE) ||
                    b->inverse_perm == nullptr ||

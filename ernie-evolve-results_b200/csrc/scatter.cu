@@ -267,6 +267,8 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
 }  // namespace
 
 int device_sms();
+cudaError_t launch_scatter_bulk(const moe_rd_params& p, const moe_rd_buffers& b, int32_t* status,
+                                cudaStream_t s);
 
 size_t positions_smem(int K, int E) { return (size_t)((kTile * K + 31) / 32) * E * 2 + 16; }
 
@@ -297,6 +299,7 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   count_launch();
   if (e != cudaSuccess) return e;
   if (plan.scatter == MOE_RD_SCATTER_NONE) return cudaSuccess;
+  if (plan.scatter == MOE_RD_SCATTER_BULK) return launch_scatter_bulk(p, b, status, s);
 
   ScatterArgs a = {};
   a.x = static_cast<const uint16_t*>(b.x);

@@ -1,0 +1,283 @@
+// Row scatter through shared memory with bulk asynchronous copies (the TMA
+// engine, non-tensor form): a token row is staged once in shared memory and
+// then written to each of its K destination rows by ONE cp.async.bulk
+// instruction per copy, so HBM sees whole-row bursts instead of 512-byte pieces
+// and the SM issues a handful of instructions per row.
+//
+// Same contract as scatter_kernel (scatter.cu), which replaces gather_body of
+// the reference (kernel.cu:2216-2238): permuted[inverse_perm[t,k], :] = x[t, :]
+// (bf16), or its fp8-e4m3 image with one fp32 scale per 128 elements.
+//
+// bf16:  one warp per CTA owns a ring of stages; lane 0 streams rows in with
+//        cp.async.bulk (global -> shared, completion on an mbarrier); lane k
+//        reads inverse_perm[t,k] while the row is in flight and, once it has
+//        landed, issues the bulk store of copy k.
+// fp8:   a CTA quantises the row cooperatively into a shared-memory image
+//        (bytes + scales, double buffered) and thread k issues the bulk stores.
+// Every mbarrier wait is bounded; on expiry the status block is set and the CTA
+// stops taking rows.
+#include <cuda_fp8.h>
+
+#include "common.cuh"
+
+namespace moe_rd {
+namespace {
+
+constexpr uint32_t kSpinLimit = 1u << 20;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+  }
+  return false;
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes,
+                                          uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst_smem), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void bulk_store(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+               "r"(src_smem), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() {
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+struct BulkArgs {
+  const uint16_t* x;
+  const int32_t* inverse_perm;
+  void* rows;
+  float* scales;
+  int32_t* status;
+  int64_t T;
+  int H, K, stages;
+};
+
+// ------------------------------ bf16 --------------------------------------
+__global__ void __launch_bounds__(32) scatter_bulk_bf16_kernel(const BulkArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  pdl_sync();
+  const int lane = threadIdx.x;
+  const uint32_t row_bytes = (uint32_t)a.H * 2;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + (size_t)a.stages * row_bytes);
+  if (lane == 0) {
+    for (int s = 0; s < a.stages; ++s) mbar_init(smem_u32(bars + s), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  const int64_t G = gridDim.x;
+  const int64_t first = blockIdx.x;
+  const unsigned char* xb = reinterpret_cast<const unsigned char*>(a.x);
+  unsigned char* out = static_cast<unsigned char*>(a.rows);
+
+  if (lane == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      const int64_t t = first + (int64_t)s * G;
+      if (t >= a.T) break;
+      const uint32_t bar = smem_u32(bars + s);
+      mbar_expect_tx(bar, row_bytes);
+      bulk_load(smem_u32(smem + (size_t)s * row_bytes), xb + (size_t)t * row_bytes, row_bytes, bar);
+    }
+  }
+  int64_t i = 0;
+  for (int64_t t = first; t < a.T; t += G, ++i) {
+    const int s = (int)(i % a.stages);
+    const uint32_t parity = (uint32_t)((i / a.stages) & 1);
+    int pos = -1;
+    if (lane < a.K) pos = __ldg(a.inverse_perm + (size_t)t * a.K + lane);
+    bool ok = mbar_wait(smem_u32(bars + s), parity);
+    ok = __all_sync(kFull, ok);
+    if (!ok) {
+      if (lane == 0) report(a.status, 301, (int)t, s);
+      break;
+    }
+    const uint32_t src = smem_u32(smem + (size_t)s * row_bytes);
+    if (pos >= 0) bulk_store(out + (size_t)pos * row_bytes, src, row_bytes);
+    bulk_commit();
+    // the stage may be refilled once every lane's stores have read it
+    bulk_wait_read<0>();
+    __syncwarp();
+    const int64_t tn = t + (int64_t)a.stages * G;
+    if (lane == 0 && tn < a.T) {
+      const uint32_t bar = smem_u32(bars + s);
+      mbar_expect_tx(bar, row_bytes);
+      bulk_load(src, xb + (size_t)tn * row_bytes, row_bytes, bar);
+    }
+  }
+  // leave only after the loads this warp started have landed (they target its shared memory)
+  if (lane == 0) {
+    for (int64_t t = first + i * G, j = i; j < i + a.stages; ++j, t += G) {
+      // rows [i, i+stages) were requested only if they exist and were not consumed above
+      if (t < a.T) mbar_wait(smem_u32(bars + (int)(j % a.stages)), (uint32_t)((j / a.stages) & 1));
+    }
+  }
+}
+
+// ------------------------------ fp8 ---------------------------------------
+constexpr int kQThreads = 128;
+
+__device__ __forceinline__ uint32_t abs_bf16x2(uint32_t v) { return v & 0x7fff7fffu; }
+__device__ __forceinline__ float amax8(const uint4& v) {
+  float m = fmaxf(bf16_lo(abs_bf16x2(v.x)), bf16_hi(abs_bf16x2(v.x)));
+  m = fmaxf(m, fmaxf(bf16_lo(abs_bf16x2(v.y)), bf16_hi(abs_bf16x2(v.y))));
+  m = fmaxf(m, fmaxf(bf16_lo(abs_bf16x2(v.z)), bf16_hi(abs_bf16x2(v.z))));
+  m = fmaxf(m, fmaxf(bf16_lo(abs_bf16x2(v.w)), bf16_hi(abs_bf16x2(v.w))));
+  return m;
+}
+__device__ __forceinline__ uint32_t quant4(uint32_t a, uint32_t b, float inv) {
+  const float2 f0 = make_float2(__fmul_rn(bf16_lo(a), inv), __fmul_rn(bf16_hi(a), inv));
+  const float2 f1 = make_float2(__fmul_rn(bf16_lo(b), inv), __fmul_rn(bf16_hi(b), inv));
+  const uint32_t q0 = __nv_cvt_float2_to_fp8x2(f0, __NV_SATFINITE, __NV_E4M3);
+  const uint32_t q1 = __nv_cvt_float2_to_fp8x2(f1, __NV_SATFINITE, __NV_E4M3);
+  return q0 | (q1 << 16);
+}
+
+// Shared image of one quantised row: H bytes, then H/128 scales (16-byte aligned).
+__global__ void __launch_bounds__(kQThreads) scatter_bulk_fp8_kernel(const BulkArgs a) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  pdl_sync();
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int n16 = a.H >> 4, nb = a.H >> 7;
+  const uint32_t q_bytes = (uint32_t)a.H;
+  const uint32_t s_bytes = (uint32_t)nb * 4;
+  const uint32_t img = (q_bytes + s_bytes + 127u) & ~127u;
+  const uint4* x4 = reinterpret_cast<const uint4*>(a.x);
+  unsigned char* out_q = static_cast<unsigned char*>(a.rows);
+  unsigned char* out_s = reinterpret_cast<unsigned char*>(a.scales);
+
+  int64_t i = 0;
+  for (int64_t t = blockIdx.x; t < a.T; t += gridDim.x, ++i) {
+    unsigned char* buf = smem + (size_t)(i & 1) * img;
+    int pos = -1;
+    if (tid < a.K) pos = __ldg(a.inverse_perm + (size_t)t * a.K + tid);
+    // the buffer used two rows ago must have been read by its stores
+    if (tid < a.K) bulk_wait_read<1>();
+    __syncthreads();
+    const uint4* src = x4 + (size_t)t * (n16 * 2);
+    for (int v0 = 0; v0 < n16; v0 += kQThreads) {
+      const int v = v0 + tid;
+      const bool act = v < n16;
+      uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+      if (act) {
+        lo = __ldg(src + 2 * v);
+        hi = __ldg(src + 2 * v + 1);
+      }
+      float am = fmaxf(amax8(lo), amax8(hi));
+      am = fmaxf(am, __shfl_xor_sync(kFull, am, 4));
+      am = fmaxf(am, __shfl_xor_sync(kFull, am, 2));
+      am = fmaxf(am, __shfl_xor_sync(kFull, am, 1));
+      const float scale = __fmul_rn(fmaxf(am, 1e-30f), 1.0f / 448.0f);
+      const float inv = __fdiv_rn(1.0f, scale);
+      uint4 q;
+      q.x = quant4(lo.x, lo.y, inv);
+      q.y = quant4(lo.z, lo.w, inv);
+      q.z = quant4(hi.x, hi.y, inv);
+      q.w = quant4(hi.z, hi.w, inv);
+      if (act) {
+        reinterpret_cast<uint4*>(buf)[v] = q;
+        if ((lane & 7) == 0) reinterpret_cast<float*>(buf + q_bytes)[v >> 3] = scale;
+      }
+    }
+    fence_async_smem();  // make this thread's shared-memory writes visible to the bulk engine
+    __syncthreads();
+    if (tid < a.K) {
+      if (pos >= 0) {
+        bulk_store(out_q + (size_t)pos * q_bytes, smem_u32(buf), q_bytes);
+        bulk_store(out_s + (size_t)pos * s_bytes, smem_u32(buf + q_bytes), s_bytes);
+      }
+      bulk_commit();
+    }
+  }
+  if (tid < a.K) bulk_wait_read<0>();
+}
+
+}  // namespace
+
+int device_sms();
+
+bool bulk_scatter_eligible(const moe_rd_params& p) {
+  if (p.T <= 0 || p.K > 32) return false;
+  if (p.rows_format == MOE_RD_ROWS_FP8_E4M3_B128)
+    return p.H % 512 == 0 && (size_t)2 * ((p.H + (p.H / 128) * 4 + 127) & ~127) <= 200 * 1024;
+  return (size_t)p.H * 2 * 2 + 64 <= 200 * 1024;
+}
+
+cudaError_t init_bulk_attributes() {
+  cudaError_t e = cudaFuncSetAttribute(scatter_bulk_bf16_kernel,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(scatter_bulk_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                              200 * 1024);
+}
+
+cudaError_t launch_scatter_bulk(const moe_rd_params& p, const moe_rd_buffers& b, int32_t* status,
+                                cudaStream_t s) {
+  BulkArgs a;
+  a.x = static_cast<const uint16_t*>(b.x);
+  a.inverse_perm = b.inverse_perm;
+  a.rows = b.permuted;
+  a.scales = b.scales;
+  a.status = status;
+  a.T = p.T;
+  a.H = p.H;
+  a.K = p.K;
+  const int sms = device_sms();
+  cudaError_t e;
+  if (p.rows_format == MOE_RD_ROWS_FP8_E4M3_B128) {
+    const size_t img = ((size_t)p.H + (p.H / 128) * 4 + 127) & ~(size_t)127;
+    const size_t smem = 2 * img;
+    int per_sm = (int)((200 * 1024) / (smem + 1024));
+    if (per_sm > 12) per_sm = 12;
+    if (per_sm < 1) per_sm = 1;
+    int64_t grid = (int64_t)sms * per_sm;
+    if (grid > p.T) grid = p.T;
+    a.stages = 2;
+    e = launch_pdl(scatter_bulk_fp8_kernel, dim3((unsigned)grid), dim3(kQThreads), smem, s, a);
+  } else {
+    const size_t row = (size_t)p.H * 2;
+    // about 160 KB of rows in flight per SM, at least 2 stages per warp
+    int stages = 4;
+    while (stages > 2 && stages * row + 64 > 48 * 1024) --stages;
+    const size_t smem = stages * row + 8 * stages;
+    int per_sm = (int)((160 * 1024) / (smem + 1024));
+    if (per_sm > 16) per_sm = 16;
+    if (per_sm < 1) per_sm = 1;
+    int64_t grid = (int64_t)sms * per_sm;
+    if (grid > p.T) grid = p.T;
+    a.stages = stages;
+    e = launch_pdl(scatter_bulk_bf16_kernel, dim3((unsigned)grid), dim3(32), smem, s, a);
+  }
+  count_launch();
+  return e;
+}
+
+}  // namespace moe_rd

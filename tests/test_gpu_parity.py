@@ -210,3 +210,12 @@ def test_round_trip_property_at_full_size():
     assert bool(((inv >= offs[ids]) & (inv < offs[ids + 1])).all())
     assert int(offs[-1]) == inv.numel()
     assert torch.equal(torch.sort(inv.reshape(-1)).values, torch.arange(inv.numel(), device="cuda"))
+
+
+@pytest.mark.parametrize("name,T,H", [("c2", None, None), ("c3", None, None), ("c4", None, None), ("c1", 37, 1024),
+                                      ("c3", 1500, 512), ("c4", 333, 1024), ("c2", 1, 4096)])
+def test_bulk_copy_scatter_matches_oracle(name, T, H):
+    """The shared-memory / bulk-copy scatter must produce the same bytes as the
+    plain one (and as the oracle), including capacity drops and fp8 scales."""
+    t, kw = workloads.make(name, T=T, H=H)
+    check(t, kw, gate_impl="simt", scatter_impl="bulk")
