@@ -228,7 +228,7 @@ def run_ours(args, rank, world, local_rank):
     w = tensors["w"].to(dev)
     bias = None if tensors["bias"] is None else tensors["bias"].to(dev)
     fused = world > 1 and args.ep == "fused"
-    sess = Session(T, H, E, K, device=dev, w_dtype=w.dtype, scatter_impl="none" if fused else "auto",
+    sess = Session(T, H, E, K, device=dev, w_dtype=w.dtype, scatter_impl="none" if fused else args.scatter,
                    **session_kwargs(kw))
     ep = None
     if world > 1:
@@ -421,6 +421,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--scatter", default="auto", choices=["auto", "simt", "bulk"])
     ap.add_argument("--ep", default="fused", choices=["fused", "nccl"],
                     help="expert-parallel exchange at N > 1: one peer-store kernel, or NCCL all-to-all + reorder")
     args = ap.parse_args()

@@ -75,6 +75,20 @@ __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
   return d;
 }
 
+// MN-major operand tile (rows = K, 64 elements of N per 128-byte row) with
+// 128-byte swizzle: the 8 K-rows of a group are 128 bytes apart, groups of 8
+// K-rows 1024 bytes apart (stride byte offset), blocks of 64 N-elements
+// `n_block_bytes` apart (leading byte offset).
+__device__ __forceinline__ uint64_t make_desc_mn(uint32_t smem_addr, uint32_t n_block_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3ffffu) >> 4);
+  d |= (uint64_t)((n_block_bytes >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
                                          uint32_t accumulate) {
   asm volatile(
@@ -94,6 +108,7 @@ struct UmmaArgs {
   int32_t* status;
   int64_t T;
   int E, kblocks, ksplit, stages, tmem_cols;
+  int w_mn_major;  // 1: map_w is over W[H,E] and B tiles are MN-major; 0: over W^T[E,H], K-major
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -156,7 +171,13 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         mbar_expect_tx(fb, stage_bytes);
         unsigned char* st = smem + (size_t)s * stage_bytes;
         tma_load_2d(smem_u32(st), &map_x, (kb0 + i) * kBlockK, mt * kBlockM, fb);
-        tma_load_2d(smem_u32(st + a_bytes), &map_w, (kb0 + i) * kBlockK, 0, fb);
+        if (a.w_mn_major) {
+          // one [64 h][64 e] box per block of 64 experts, 8 KB apart
+          for (int nb = 0; nb < a.E / 64; ++nb)
+            tma_load_2d(smem_u32(st + a_bytes + nb * 8192), &map_w, nb * 64, (kb0 + i) * kBlockK, fb);
+        } else {
+          tma_load_2d(smem_u32(st + a_bytes), &map_w, (kb0 + i) * kBlockK, 0, fb);
+        }
         issued = i + 1;
       }
       if (*abort_flag) {
@@ -171,7 +192,8 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (lane == 0) {
       // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.E >> 3) << 17) |
-                             ((uint32_t)(kBlockM >> 4) << 24);
+                             ((uint32_t)(kBlockM >> 4) << 24) |
+                             (a.w_mn_major ? (1u << 16) : 0u);  // B major: 0 = K, 1 = MN
       bool ok = true;
       for (int i = 0; i < nkb && ok; ++i) {
         const int s = i % a.stages;
@@ -185,12 +207,15 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         unsigned char* st = smem + (size_t)s * stage_bytes;
         const uint64_t da = make_desc(smem_u32(st));
-        const uint64_t db = make_desc(smem_u32(st + a_bytes));
+        const uint64_t db = a.w_mn_major ? make_desc_mn(smem_u32(st + a_bytes), 8192u)
+                                         : make_desc(smem_u32(st + a_bytes));
 #pragma unroll
         for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-          // advance 16 elements = 32 bytes inside the 128-byte swizzle row
+          // K-major: 16 elements = 32 bytes inside the 128-byte swizzle row;
+          // MN-major: 16 K-rows = two 1024-byte groups
           const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);
-          umma_f16(tmem_base, da + step, db + step, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          const uint64_t step_b = a.w_mn_major ? (uint64_t)((k * 2048) >> 4) : step;
+          umma_f16(tmem_base, da + step, db + step_b, idesc, (i > 0 || k > 0) ? 1u : 0u);
         }
         umma_commit(smem_u32(empty_bar + s));  // frees the stage once these MMAs have read it
       }
@@ -300,6 +325,7 @@ EncodeTiledFn encode_fn() {
 
 // rows x cols bf16, row-major; box = box_rows x 64 columns, 128-byte swizzle.
 bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+  if (rows == 0 || cols == 0 || (cols * 2) % 16 != 0) return false;
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr) return false;
   const cuuint64_t dims[2] = {cols, rows};
@@ -335,7 +361,10 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
                              cudaStream_t s) {
   (void)logits;
   const uint16_t* w_eh = static_cast<const uint16_t*>(b.gate_w);
-  if (p.w_layout == MOE_RD_W_LAYOUT_HE) {
+  // W[H,E] with whole blocks of 64 experts is consumed in place as an MN-major
+  // operand; otherwise it is transposed to the K-major W^T[E,H] first.
+  const bool mn_major = p.w_layout == MOE_RD_W_LAYOUT_HE && p.E % 64 == 0;
+  if (p.w_layout == MOE_RD_W_LAYOUT_HE && !mn_major) {
     const dim3 grid((unsigned)((p.H + 31) / 32), (unsigned)((p.E + 31) / 32));
     transpose_w_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(b.gate_w),
                                             static_cast<uint16_t*>(wt), p.H, p.E);
@@ -345,8 +374,9 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
     w_eh = static_cast<const uint16_t*>(wt);
   }
   CUtensorMap map_x, map_w;
-  if (!make_map(&map_x, b.x, (uint64_t)p.T, (uint64_t)p.H, kBlockM) ||
-      !make_map(&map_w, w_eh, (uint64_t)p.E, (uint64_t)p.H, (uint32_t)p.E))
+  if (!make_map(&map_x, b.x, (uint64_t)p.T, (uint64_t)p.H, kBlockM)) return cudaErrorInvalidValue;
+  if (mn_major ? !make_map(&map_w, b.gate_w, (uint64_t)p.H, (uint64_t)p.E, 64u)
+               : !make_map(&map_w, w_eh, (uint64_t)p.E, (uint64_t)p.H, (uint32_t)p.E))
     return cudaErrorInvalidValue;
   UmmaArgs a;
   a.partial = partial;
@@ -356,6 +386,7 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
   a.kblocks = p.H / kBlockK;
   a.ksplit = plan.ksplit;
   a.stages = pick_stages(p.E);
+  a.w_mn_major = mn_major ? 1 : 0;
   int cols = 32;
   while (cols < p.E) cols <<= 1;
   a.tmem_cols = cols;

@@ -131,9 +131,8 @@ struct ScatterArgs {
 
 // Destination of pair (t,k): local row index, or (peer buffer, row) when EP.
 template <bool EP>
-__device__ __forceinline__ bool resolve_dest(const ScatterArgs& a, int64_t t, int k, void*& rows,
-                                             float*& scales, int64_t& row) {
-  const int q = __ldg(a.inverse_perm + (size_t)t * a.K + k);
+__device__ __forceinline__ bool resolve_dest(const ScatterArgs& a, int64_t t, int k, int q,
+                                             void*& rows, float*& scales, int64_t& row) {
   if (q < 0) return false;
   if (!EP) {
     rows = a.rows;
@@ -211,15 +210,29 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
 #pragma unroll
       for (int u = 0; u < 4; ++u)
         if (vb + 32 * u < nvec) val[u] = __ldg(src + vb + 32 * u);
-      for (int k = 0; k < a.K; ++k) {
-        void* rows;
-        float* scl;
-        int64_t q;
-        if (!resolve_dest<EP>(a, wk.t, k, rows, scl, q)) continue;
-        uint4* d = reinterpret_cast<uint4*>(rows) + (size_t)q * nvec;
+      // the row's destinations are fetched while its loads are in flight
+      int qv[8];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (vb + 32 * u < nvec) __stcs(d + vb + 32 * u, val[u]);
+      for (int k = 0; k < 8; ++k)
+        qv[k] = k < a.K ? __ldg(a.inverse_perm + (size_t)wk.t * a.K + k) : -1;
+#pragma unroll 1
+      for (int kb = 0; kb < a.K; kb += 8) {
+        if (kb) {
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            qv[k] = kb + k < a.K ? __ldg(a.inverse_perm + (size_t)wk.t * a.K + kb + k) : -1;
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          void* rows;
+          float* scl;
+          int64_t q;
+          if (!resolve_dest<EP>(a, wk.t, kb + k, qv[k], rows, scl, q)) continue;
+          uint4* d = reinterpret_cast<uint4*>(rows) + (size_t)q * nvec;
+#pragma unroll
+          for (int u = 0; u < 4; ++u)
+            if (vb + 32 * u < nvec) __stcs(d + vb + 32 * u, val[u]);
+        }
       }
     }
   } else {
@@ -239,6 +252,10 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
         lo = __ldg(src);
         hi = __ldg(src + 1);
       }
+      int qv[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        qv[k] = k < a.K ? __ldg(a.inverse_perm + (size_t)wk.t * a.K + k) : -1;
       float am = fmaxf(amax8(lo), amax8(hi));
       am = fmaxf(am, __shfl_xor_sync(kFull, am, 4));
       am = fmaxf(am, __shfl_xor_sync(kFull, am, 2));
@@ -251,13 +268,22 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
       q.z = quant4(hi.x, hi.y, inv);
       q.w = quant4(hi.z, hi.w, inv);
       if (act) {
-        for (int k = 0; k < a.K; ++k) {
-          void* rows;
-          float* scl;
-          int64_t r;
-          if (!resolve_dest<EP>(a, wk.t, k, rows, scl, r)) continue;
-          __stcs(reinterpret_cast<uint4*>(rows) + (size_t)r * n16 + v, q);
-          if ((lane & 7) == 0) scl[(size_t)r * nb + (v >> 3)] = scale;
+#pragma unroll 1
+        for (int kb = 0; kb < a.K; kb += 8) {
+          if (kb) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              qv[k] = kb + k < a.K ? __ldg(a.inverse_perm + (size_t)wk.t * a.K + kb + k) : -1;
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            void* rows;
+            float* scl;
+            int64_t r;
+            if (!resolve_dest<EP>(a, wk.t, kb + k, qv[k], rows, scl, r)) continue;
+            __stcs(reinterpret_cast<uint4*>(rows) + (size_t)r * n16 + v, q);
+            if ((lane & 7) == 0) scl[(size_t)r * nb + (v >> 3)] = scale;
+          }
         }
       }
     }
