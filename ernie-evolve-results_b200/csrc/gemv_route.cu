@@ -21,9 +21,15 @@
 namespace moe_rd {
 namespace {
 
-constexpr int kGemvThreads = 512;
-constexpr int kGemvWarps = kGemvThreads / 32;
 constexpr int kMaxDynSmem = 227 * 1024;
+
+// Tokens a warp carries at once and threads per block, per padded expert count:
+// 2 * TPW * EB accumulator registers per lane.  (Two tokens per warp with 1024
+// threads spills at 64 registers and measured 35 % slower on E = 8.)
+template <int EB> struct GemvShape;
+template <> struct GemvShape<8> { static constexpr int TPW = 4, THREADS = 512; };
+template <> struct GemvShape<16> { static constexpr int TPW = 2, THREADS = 512; };
+template <> struct GemvShape<32> { static constexpr int TPW = 1, THREADS = 512; };
 
 typedef unsigned long long u64;
 
@@ -69,9 +75,11 @@ __device__ __forceinline__ int staged_index(int h, int e) {
 }
 
 template <int EB, int WD>
-__global__ void __launch_bounds__(kGemvThreads, 1) gemv_route_kernel(const GemvArgs g,
-                                                                    const RouteArgs a) {
-  constexpr int TPW = 32 / EB;  // tokens a warp carries at once
+__global__ void __launch_bounds__(GemvShape<EB>::THREADS, 1)
+gemv_route_kernel(const GemvArgs g, const RouteArgs a) {
+  constexpr int TPW = GemvShape<EB>::TPW;
+  constexpr int kGemvThreads = GemvShape<EB>::THREADS;
+  constexpr int kGemvWarps = kGemvThreads / 32;
   pdl_sync();
   extern __shared__ __align__(16) unsigned char smem[];
   float* s_wf = reinterpret_cast<float*>(smem);
@@ -230,10 +238,13 @@ int pick_eb(int E) { return E <= 8 ? 8 : E <= 16 ? 16 : 32; }
 template <int EB, int WD>
 cudaError_t launch_t(const moe_rd_params& p, const GemvArgs& g, const RouteArgs& a,
                      cudaStream_t s) {
+  constexpr int TPW = GemvShape<EB>::TPW;
+  constexpr int kGemvThreads = GemvShape<EB>::THREADS;
+  constexpr int kGemvWarps = kGemvThreads / 32;
   const size_t smem = staged_w_bytes(p.H, EB) + 128;
-  const int64_t units = (p.T + 32 / EB - 1) / (32 / EB);
+  const int64_t units = (p.T + TPW - 1) / TPW;
   const int64_t need = (units + kGemvWarps - 1) / kGemvWarps;
-  const int64_t cap = device_sms();  // one 512-thread block per SM (128 registers per thread)
+  const int64_t cap = device_sms();  // one block per SM (it fills the register file)
   const int grid = (int)(need < cap ? need : cap);
   const cudaError_t e =
       launch_pdl(gemv_route_kernel<EB, WD>, dim3((unsigned)grid), dim3(kGemvThreads), smem, s, g, a);

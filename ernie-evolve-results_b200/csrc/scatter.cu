@@ -28,8 +28,30 @@
 namespace moe_rd {
 namespace {
 
-constexpr int kScatterThreads = 256;
+// Tuning constants of the streaming scatter (defaults are the measured best).
+#ifndef MOE_RD_SC_THREADS
+#define MOE_RD_SC_THREADS 256
+#endif
+#ifndef MOE_RD_SC_UNIT_VECS   // 16-byte loads per lane and bf16 work unit
+#define MOE_RD_SC_UNIT_VECS 4
+#endif
+#ifndef MOE_RD_SC_BLOCKS_PER_SM
+#define MOE_RD_SC_BLOCKS_PER_SM 64  // far more blocks than fit: late blocks fill the gaps
+#endif
+#ifndef MOE_RD_SC_STREAMING   // 1: st.global.cs (evict-first) for the row stores
+#define MOE_RD_SC_STREAMING 1
+#endif
+constexpr int kScatterThreads = MOE_RD_SC_THREADS;
 constexpr int kScatterWarps = kScatterThreads / 32;
+constexpr int kUV = MOE_RD_SC_UNIT_VECS;
+
+__device__ __forceinline__ void store_row16(uint4* p, const uint4& v) {
+#if MOE_RD_SC_STREAMING
+  __stcs(p, v);
+#else
+  *p = v;
+#endif
+}
 
 struct PositionArgs {
   const int32_t* ids;
@@ -198,17 +220,17 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
   const int64_t W = (int64_t)gridDim.x * kScatterWarps;
 
   if (FMT == MOE_RD_ROWS_BF16) {
-    // unit = 128 uint4 (2 KB) of a row: four 16-byte loads per lane
+    // unit = 32*kUV uint4 (2 KB for kUV = 4) of a row: kUV 16-byte loads per lane
     const int nvec = a.H >> 3;
-    const int upr = (nvec + 127) >> 7;
+    const int upr = (nvec + 32 * kUV - 1) / (32 * kUV);
     const uint4* x4 = reinterpret_cast<const uint4*>(a.x);
     UnitWalk wk(w0, W, upr);
     for (; wk.t < a.T; wk.next()) {
       const uint4* src = x4 + (size_t)wk.t * nvec;
-      const int vb = wk.c * 128 + lane;
-      uint4 val[4];
+      const int vb = wk.c * (32 * kUV) + lane;
+      uint4 val[kUV];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
+      for (int u = 0; u < kUV; ++u)
         if (vb + 32 * u < nvec) val[u] = __ldg(src + vb + 32 * u);
       // the row's destinations are fetched while its loads are in flight
       int qv[8];
@@ -230,8 +252,8 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
           if (!resolve_dest<EP>(a, wk.t, kb + k, qv[k], rows, scl, q)) continue;
           uint4* d = reinterpret_cast<uint4*>(rows) + (size_t)q * nvec;
 #pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (vb + 32 * u < nvec) __stcs(d + vb + 32 * u, val[u]);
+          for (int u = 0; u < kUV; ++u)
+            if (vb + 32 * u < nvec) store_row16(d + vb + 32 * u, val[u]);
         }
       }
     }
@@ -281,7 +303,7 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
             float* scl;
             int64_t r;
             if (!resolve_dest<EP>(a, wk.t, kb + k, qv[k], rows, scl, r)) continue;
-            __stcs(reinterpret_cast<uint4*>(rows) + (size_t)r * n16 + v, q);
+            store_row16(reinterpret_cast<uint4*>(rows) + (size_t)r * n16 + v, q);
             if ((lane & 7) == 0) scl[(size_t)r * nb + (v >> 3)] = scale;
           }
         }
@@ -336,10 +358,10 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   a.H = p.H;
   a.K = p.K;
   const bool fp8 = p.rows_format == MOE_RD_ROWS_FP8_E4M3_B128;
-  const int64_t upr = fp8 ? ((p.H >> 4) + 31) >> 5 : ((p.H >> 3) + 127) >> 7;
+  const int64_t upr = fp8 ? ((p.H >> 4) + 31) >> 5 : ((p.H >> 3) + 32 * kUV - 1) / (32 * kUV);
   const int64_t units = p.T * upr;
   const int64_t want = (units + kScatterWarps - 1) / kScatterWarps;
-  const int64_t cap = (int64_t)device_sms() * 8;  // 8 resident blocks of 256 threads per SM
+  const int64_t cap = (int64_t)device_sms() * MOE_RD_SC_BLOCKS_PER_SM;
   const unsigned grid = (unsigned)(want < cap ? want : cap);
   if (fp8)
     e = launch_pdl(scatter_kernel<MOE_RD_ROWS_FP8_E4M3_B128, false>, dim3(grid), dim3(kScatterThreads), 0, s, a);
@@ -442,10 +464,10 @@ extern "C" int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const in
     a.peer_scales[d] = fp8 ? peer_scales[d] : nullptr;
     if (fp8 && a.peer_scales[d] == nullptr) return MOE_RD_E_NULL;
   }
-  const int64_t upr = fp8 ? ((p->H >> 4) + 31) >> 5 : ((p->H >> 3) + 127) >> 7;
+  const int64_t upr = fp8 ? ((p->H >> 4) + 31) >> 5 : ((p->H >> 3) + 32 * kUV - 1) / (32 * kUV);
   const int64_t units = p->T * upr;
   const int64_t want = (units + kScatterWarps - 1) / kScatterWarps;
-  const int64_t cap = (int64_t)device_sms() * 8;
+  const int64_t cap = (int64_t)device_sms() * MOE_RD_SC_BLOCKS_PER_SM;
   const unsigned grid = (unsigned)(want < cap ? want : cap);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
