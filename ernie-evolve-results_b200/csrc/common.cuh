@@ -42,6 +42,7 @@ struct Plan {
   int gate;        // resolved MOE_RD_GATE_*
   int scatter;     // resolved MOE_RD_SCATTER_*
   int ksplit;      // split-K factor of the tensor-core gate
+  int umma_mh;     // 128-token halves per CTA of the tensor-core gate (1 or 2)
 };
 
 int make_plan(const moe_rd_params& p, Plan* plan);

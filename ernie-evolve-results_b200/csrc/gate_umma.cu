@@ -109,6 +109,7 @@ struct UmmaArgs {
   int64_t T;
   int E, kblocks, ksplit, stages, tmem_cols;
   int w_mn_major;  // 1: map_w is over W[H,E] and B tiles are MN-major; 0: over W^T[E,H], K-major
+  int mh;          // 128-token halves per CTA (1 or 2): two halves share every W tile
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -118,7 +119,8 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   // 1024-byte alignment for the swizzled tiles
   unsigned char* smem = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  const uint32_t a_bytes = kBlockM * kBlockK * 2;
+  const uint32_t half_bytes = kBlockM * kBlockK * 2;
+  const uint32_t a_bytes = (uint32_t)a.mh * half_bytes;
   const uint32_t b_bytes = (uint32_t)a.E * kBlockK * 2;
   const uint32_t stage_bytes = a_bytes + b_bytes;
   unsigned char* tail = smem + (size_t)a.stages * stage_bytes;
@@ -170,7 +172,9 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         const uint32_t fb = smem_u32(full_bar + s);
         mbar_expect_tx(fb, stage_bytes);
         unsigned char* st = smem + (size_t)s * stage_bytes;
-        tma_load_2d(smem_u32(st), &map_x, (kb0 + i) * kBlockK, mt * kBlockM, fb);
+        for (int h = 0; h < a.mh; ++h)
+          tma_load_2d(smem_u32(st + h * half_bytes), &map_x, (kb0 + i) * kBlockK,
+                      (mt * a.mh + h) * kBlockM, fb);
         if (a.w_mn_major) {
           // one [64 h][64 e] box per block of 64 experts, 8 KB apart
           for (int nb = 0; nb < a.E / 64; ++nb)
@@ -206,7 +210,8 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         unsigned char* st = smem + (size_t)s * stage_bytes;
-        const uint64_t da = make_desc(smem_u32(st));
+        const uint64_t da0 = make_desc(smem_u32(st));
+        const uint64_t da1 = make_desc(smem_u32(st + half_bytes));
         const uint64_t db = a.w_mn_major ? make_desc_mn(smem_u32(st + a_bytes), 8192u)
                                          : make_desc(smem_u32(st + a_bytes));
 #pragma unroll
@@ -215,7 +220,10 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
           // MN-major: 16 K-rows = two 1024-byte groups
           const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);
           const uint64_t step_b = a.w_mn_major ? (uint64_t)((k * 2048) >> 4) : step;
-          umma_f16(tmem_base, da + step, db + step_b, idesc, (i > 0 || k > 0) ? 1u : 0u);
+          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+          umma_f16(tmem_base, da0 + step, db + step_b, idesc, acc);
+          // the second 128-token half accumulates E columns further on
+          if (a.mh == 2) umma_f16(tmem_base + (uint32_t)a.E, da1 + step, db + step_b, idesc, acc);
         }
         umma_commit(smem_u32(empty_bar + s));  // frees the stage once these MMAs have read it
       }
@@ -231,11 +239,12 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       *abort_flag = 1;
     } else {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int64_t row = (int64_t)mt * kBlockM + q * 32 + lane;
+      for (int h = 0; h < a.mh; ++h) {
+      const int64_t row = ((int64_t)mt * a.mh + h) * kBlockM + q * 32 + lane;
       float* out = a.partial + ((size_t)ks * a.T + (row < a.T ? row : 0)) * a.E;
       for (int c = 0; c < a.E; c += 32) {
         uint32_t r[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * a.E + c);
         if (a.E - c >= 32) {
           asm volatile(
               "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -272,6 +281,7 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
               o4[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
                                   __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
         }
+      }
       }
     }
   }
@@ -337,14 +347,18 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, ui
             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-int pick_stages(int E) {
-  const int stage = kBlockM * kBlockK * 2 + E * kBlockK * 2;
-  int s = (200 * 1024) / stage;
+// One CTA per SM with two token halves (or with E = 256); two CTAs per SM for a
+// single half and few experts, so that more than 148 tiles stay resident.
+int pick_stages(int E, int mh) {
+  const int stage = mh * kBlockM * kBlockK * 2 + E * kBlockK * 2;
+  const int budget = (mh == 2 || E > 128) ? 200 * 1024 : 100 * 1024;
+  int s = budget / stage;
   return s > 8 ? 8 : (s < 2 ? 2 : s);
 }
 
-size_t umma_smem_bytes(int E, int stages) {
-  return (size_t)stages * (kBlockM * kBlockK * 2 + E * kBlockK * 2) + (2 * stages + 1) * 8 + 16 + 1024;
+size_t umma_smem_bytes(int E, int stages, int mh) {
+  return (size_t)stages * (mh * kBlockM * kBlockK * 2 + E * kBlockK * 2) + (2 * stages + 1) * 8 + 16 +
+         1024;
 }
 
 }  // namespace
@@ -385,13 +399,15 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
   a.E = p.E;
   a.kblocks = p.H / kBlockK;
   a.ksplit = plan.ksplit;
-  a.stages = pick_stages(p.E);
+  a.mh = plan.umma_mh;
+  a.stages = pick_stages(p.E, a.mh);
   a.w_mn_major = mn_major ? 1 : 0;
   int cols = 32;
-  while (cols < p.E) cols <<= 1;
+  while (cols < p.E * a.mh) cols <<= 1;
   a.tmem_cols = cols;
-  const dim3 grid((unsigned)((p.T + kBlockM - 1) / kBlockM), (unsigned)plan.ksplit);
-  gate_umma_kernel<<<grid, kThreads, umma_smem_bytes(p.E, a.stages), s>>>(map_x, map_w, a);
+  const int tile = kBlockM * a.mh;
+  const dim3 grid((unsigned)((p.T + tile - 1) / tile), (unsigned)plan.ksplit);
+  gate_umma_kernel<<<grid, kThreads, umma_smem_bytes(p.E, a.stages, a.mh), s>>>(map_x, map_w, a);
   count_launch();
   return cudaGetLastError();
 }

@@ -45,12 +45,16 @@ int make_plan(const moe_rd_params& p, Plan* plan) {
   // Split K only when the token tiles alone cannot fill the SMs (148): every
   // split writes and re-reads a [T,E] fp32 partial, which costs more than a
   // ragged last wave once there is at least one full wave of tiles.
-  int ksplit = 1;
+  int ksplit = 1, mh = 1;
   if (gate == MOE_RD_GATE_UMMA) {
-    const int64_t mtiles = (p.T + 127) / 128;
+    // two 128-token halves per CTA share every weight tile (half the L2 reads of
+    // W) once there are enough tokens to still fill the SMs
+    mh = (p.T >= 4096 && p.E <= 128) ? 2 : 1;  // at E = 256 it measured no faster and doubles the splits
+    const int64_t mtiles = (p.T + 128 * mh - 1) / (128 * mh);
     const int kblocks = p.H / 64;
     while (ksplit < 8 && mtiles * ksplit * 2 <= 148 && kblocks / (ksplit * 2) >= 4) ksplit *= 2;
   }
+  plan->umma_mh = mh;
   plan->ksplit = ksplit;
   return MOE_RD_OK;
 }
