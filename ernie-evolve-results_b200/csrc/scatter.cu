@@ -226,7 +226,10 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
     const uint4* x4 = reinterpret_cast<const uint4*>(a.x);
     UnitWalk wk(w0, W, upr);
     for (; wk.t < a.T; wk.next()) {
-      const uint4* src = x4 + (size_t)wk.t * nvec;
+      // Rows are taken last-first: the gate pass read x in ascending order just
+      // before, so the tail of x is what is most likely still in L2.
+      const int64_t t = a.T - 1 - wk.t;
+      const uint4* src = x4 + (size_t)t * nvec;
       const int vb = wk.c * (32 * kUV) + lane;
       uint4 val[kUV];
 #pragma unroll
@@ -236,20 +239,20 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
       int qv[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k)
-        qv[k] = k < a.K ? __ldg(a.inverse_perm + (size_t)wk.t * a.K + k) : -1;
+        qv[k] = k < a.K ? __ldg(a.inverse_perm + (size_t)t * a.K + k) : -1;
 #pragma unroll 1
       for (int kb = 0; kb < a.K; kb += 8) {
         if (kb) {
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            qv[k] = kb + k < a.K ? __ldg(a.inverse_perm + (size_t)wk.t * a.K + kb + k) : -1;
+            qv[k] = kb + k < a.K ? __ldg(a.inverse_perm + (size_t)t * a.K + kb + k) : -1;
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           void* rows;
           float* scl;
           int64_t q;
-          if (!resolve_dest<EP>(a, wk.t, kb + k, qv[k], rows, scl, q)) continue;
+          if (!resolve_dest<EP>(a, t, kb + k, qv[k], rows, scl, q)) continue;
           uint4* d = reinterpret_cast<uint4*>(rows) + (size_t)q * nvec;
 #pragma unroll
           for (int u = 0; u < kUV; ++u)
@@ -266,18 +269,19 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
     const uint4* x4 = reinterpret_cast<const uint4*>(a.x);
     UnitWalk wk(w0, W, upr);
     for (; wk.t < a.T; wk.next()) {
+      const int64_t t = a.T - 1 - wk.t;  // last rows first (see above)
       const int v = wk.c * 32 + lane;
       const bool act = v < n16;
       uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
       if (act) {
-        const uint4* src = x4 + (size_t)wk.t * (n16 * 2) + 2 * v;
+        const uint4* src = x4 + (size_t)t * (n16 * 2) + 2 * v;
         lo = __ldg(src);
         hi = __ldg(src + 1);
       }
       int qv[8];
 #pragma unroll
       for (int k = 0; k < 8; ++k)
-        qv[k] = k < a.K ? __ldg(a.inverse_perm + (size_t)wk.t * a.K + k) : -1;
+        qv[k] = k < a.K ? __ldg(a.inverse_perm + (size_t)t * a.K + k) : -1;
       float am = fmaxf(amax8(lo), amax8(hi));
       am = fmaxf(am, __shfl_xor_sync(kFull, am, 4));
       am = fmaxf(am, __shfl_xor_sync(kFull, am, 2));
@@ -295,14 +299,14 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
           if (kb) {
 #pragma unroll
             for (int k = 0; k < 8; ++k)
-              qv[k] = kb + k < a.K ? __ldg(a.inverse_perm + (size_t)wk.t * a.K + kb + k) : -1;
+              qv[k] = kb + k < a.K ? __ldg(a.inverse_perm + (size_t)t * a.K + kb + k) : -1;
           }
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             void* rows;
             float* scl;
             int64_t r;
-            if (!resolve_dest<EP>(a, wk.t, kb + k, qv[k], rows, scl, r)) continue;
+            if (!resolve_dest<EP>(a, t, kb + k, qv[k], rows, scl, r)) continue;
             store_row16(reinterpret_cast<uint4*>(rows) + (size_t)r * n16 + v, q);
             if ((lane & 7) == 0) scl[(size_t)r * nb + (v >> 3)] = scale;
           }

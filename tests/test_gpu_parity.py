@@ -125,6 +125,8 @@ def test_odd_expert_count_scalar_weight_path():
     dict(E=128, K=8, score_fn="softmax", n_groups=2, topk_groups=1, group_topk=1),
     dict(E=256, K=32, score_fn="softmax"),
     dict(E=32, K=1, score_fn="softmax", renorm=False),
+    dict(E=160, K=12, score_fn="softmax", n_groups=5, topk_groups=2, group_topk=4),
+    dict(E=72, K=3, score_fn="sigmoid", n_groups=8, topk_groups=5, group_topk=1),
 ])
 def test_routing_modes_on_given_logits_with_ties(case):
     """Logits are supplied, so only scoring/selection/dispatch run; rows of
