@@ -27,6 +27,20 @@ constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
 constexpr uint32_t kSpinLimit = 1u << 20;
 
+// Tuning constants (defaults are the measured best).
+#ifndef MOE_RD_UMMA_L2_PROMOTION
+#define MOE_RD_UMMA_L2_PROMOTION CU_TENSOR_MAP_L2_PROMOTION_L2_128B
+#endif
+#ifndef MOE_RD_UMMA_SMEM_KB_ONE_CTA   // shared-memory budget when one CTA owns the SM
+#define MOE_RD_UMMA_SMEM_KB_ONE_CTA 200
+#endif
+#ifndef MOE_RD_UMMA_SMEM_KB_TWO_CTA   // ... when two CTAs share it
+#define MOE_RD_UMMA_SMEM_KB_TWO_CTA 100
+#endif
+#ifndef MOE_RD_UMMA_TWO_CTA_MAX_E     // largest E for which two CTAs per SM are targeted
+#define MOE_RD_UMMA_TWO_CTA_MAX_E 128
+#endif
+
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
@@ -344,14 +358,15 @@ bool make_map(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, ui
   const cuuint32_t estr[2] = {1, 1};
   return fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
             estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+            MOE_RD_UMMA_L2_PROMOTION, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // One CTA per SM with two token halves (or with E = 256); two CTAs per SM for a
 // single half and few experts, so that more than 148 tiles stay resident.
 int pick_stages(int E, int mh) {
   const int stage = mh * kBlockM * kBlockK * 2 + E * kBlockK * 2;
-  const int budget = (mh == 2 || E > 128) ? 200 * 1024 : 100 * 1024;
+  const int budget = (mh == 2 || E > MOE_RD_UMMA_TWO_CTA_MAX_E) ? MOE_RD_UMMA_SMEM_KB_ONE_CTA * 1024
+                                                                 : MOE_RD_UMMA_SMEM_KB_TWO_CTA * 1024;
   int s = budget / stage;
   return s > 8 ? 8 : (s < 2 ? 2 : s);
 }
