@@ -233,7 +233,9 @@ def run_ours(args, rank, world, local_rank):
     ep = None
     if world > 1:
         from moe_rd.ep import ExpertParallel, ExpertParallelFused
-        ep = ExpertParallelFused(sess, dist.group.WORLD) if fused else ExpertParallel(sess, dist.group.WORLD)
+        ep = (ExpertParallelFused(sess, dist.group.WORLD,
+                                  bulk={"auto": None, "bulk": True, "simt": False}[args.scatter]) if fused
+              else ExpertParallel(sess, dist.group.WORLD))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
     def step():
@@ -329,7 +331,9 @@ def run_ours(args, rank, world, local_rank):
                   "frac_of_900": max(egress / 900.0 / 1e6, op_bytes / peak / 1e6) / step_ms, "mode": args.ep}
     clocks = sampler.stop() if rank == 0 else None
     if fused:
-        roofline = {"bound": "nvlink", "kernel": "scatter_kernel<EP> (peer stores)",
+        roofline = {"bound": "nvlink",
+                    "kernel": "scatter_bulk_fp8_kernel<EP> (cp.async.bulk peer stores)" if ep.bulk
+                    else "scatter_kernel<EP> (16-byte peer stores)",
                     "achieved": nvlink["exchange_gbs"], "peak": nvlink["link_peak_gbs"], "unit": "GB/s",
                     "frac": nvlink["exchange_gbs"] / nvlink["link_peak_gbs"],
                     "peak_kind": nvlink["link_peak_kind"], "traffic": None,

@@ -321,6 +321,11 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
 int device_sms();
 cudaError_t launch_scatter_bulk(const moe_rd_params& p, const moe_rd_buffers& b, int32_t* status,
                                 cudaStream_t s);
+cudaError_t launch_scatter_bulk_ep(const moe_rd_params& p, const void* x, const int32_t* ids,
+                                   const int32_t* inverse_perm, const int32_t* offsets,
+                                   const int32_t* dest_base, int world, void* const* peer_rows,
+                                   float* const* peer_scales, int32_t* status, cudaStream_t s);
+bool bulk_scatter_eligible(const moe_rd_params& p);
 
 size_t positions_smem(int K, int E) { return (size_t)((kTile * K + 31) / 32) * E * 2 + 16; }
 
@@ -442,7 +447,7 @@ extern "C" int moe_rd_ep_plan(const int32_t* kept_all, int world, int rank, int 
 extern "C" int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const int32_t* expert_ids,
                                  const int32_t* inverse_perm, const int32_t* offsets,
                                  const int32_t* dest_base, int world, void* const* peer_rows,
-                                 float* const* peer_scales, void* stream) {
+                                 float* const* peer_scales, int32_t* status, void* stream) {
   if (p == nullptr || x == nullptr || expert_ids == nullptr || inverse_perm == nullptr ||
       offsets == nullptr || dest_base == nullptr || peer_rows == nullptr)
     return MOE_RD_E_NULL;
@@ -451,6 +456,19 @@ extern "C" int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const in
   const bool fp8 = p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128;
   if (fp8 && (peer_scales == nullptr || p->H % 128 != 0)) return MOE_RD_E_NULL;
   if (p->T == 0) return MOE_RD_OK;
+  if (p->scatter_impl == MOE_RD_SCATTER_BULK) {
+    // whole-row bulk copies (TMA engine) into the owners' buffers
+    if (!bulk_scatter_eligible(*p)) return MOE_RD_E_UNSUPPORTED;
+    for (int d = 0; d < world; ++d)
+      if ((reinterpret_cast<uintptr_t>(peer_rows[d]) & 15) ||
+          (fp8 && (reinterpret_cast<uintptr_t>(peer_scales[d]) & 15)))
+        return MOE_RD_E_ALIGN;
+    if (status == nullptr) return MOE_RD_E_NULL;
+    const cudaError_t be =
+        launch_scatter_bulk_ep(*p, x, expert_ids, inverse_perm, offsets, dest_base, world, peer_rows,
+                               peer_scales, status, static_cast<cudaStream_t>(stream));
+    return be == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
+  }
   ScatterArgs a = {};
   a.x = static_cast<const uint16_t*>(x);
   a.inverse_perm = inverse_perm;

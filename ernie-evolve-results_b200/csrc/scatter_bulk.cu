@@ -72,6 +72,8 @@ __device__ __forceinline__ void fence_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
 
+constexpr int kMaxWorld = 8;
+
 struct BulkArgs {
   const uint16_t* x;
   const int32_t* inverse_perm;
@@ -80,9 +82,35 @@ struct BulkArgs {
   int32_t* status;
   int64_t T;
   int H, K, stages;
+  // expert-parallel destinations (see ScatterArgs in scatter.cu)
+  const int32_t* ids;
+  const int32_t* offsets;
+  const int32_t* dest_base;
+  void* peer_rows[kMaxWorld];
+  float* peer_scales[kMaxWorld];
+  int epr;
 };
 
+// Destination of pair (t,k) with local row q >= 0: buffers and row to write.
+template <bool EP>
+__device__ __forceinline__ void bulk_dest(const BulkArgs& a, int64_t t, int k, int q,
+                                          unsigned char*& rows, unsigned char*& scales,
+                                          int64_t& row) {
+  if (!EP) {
+    rows = static_cast<unsigned char*>(a.rows);
+    scales = reinterpret_cast<unsigned char*>(a.scales);
+    row = q;
+    return;
+  }
+  const int e = __ldg(a.ids + (size_t)t * a.K + k);
+  const int d = e / a.epr;
+  rows = static_cast<unsigned char*>(a.peer_rows[d]);
+  scales = reinterpret_cast<unsigned char*>(a.peer_scales[d]);
+  row = (int64_t)__ldg(a.dest_base + e) + (q - __ldg(a.offsets + e));
+}
+
 // ------------------------------ bf16 --------------------------------------
+template <bool EP>
 __global__ void __launch_bounds__(32) scatter_bulk_bf16_kernel(const BulkArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_sync();
@@ -97,7 +125,6 @@ __global__ void __launch_bounds__(32) scatter_bulk_bf16_kernel(const BulkArgs a)
   const int64_t G = gridDim.x;
   const int64_t first = blockIdx.x;
   const unsigned char* xb = reinterpret_cast<const unsigned char*>(a.x);
-  unsigned char* out = static_cast<unsigned char*>(a.rows);
 
   if (lane == 0) {
     for (int s = 0; s < a.stages; ++s) {
@@ -121,7 +148,12 @@ __global__ void __launch_bounds__(32) scatter_bulk_bf16_kernel(const BulkArgs a)
       break;
     }
     const uint32_t src = smem_u32(smem + (size_t)s * row_bytes);
-    if (pos >= 0) bulk_store(out + (size_t)pos * row_bytes, src, row_bytes);
+    if (pos >= 0) {
+      unsigned char *out, *unused;
+      int64_t r;
+      bulk_dest<EP>(a, t, lane, pos, out, unused, r);
+      bulk_store(out + (size_t)r * row_bytes, src, row_bytes);
+    }
     bulk_commit();
     // the stage may be refilled once every lane's stores have read it
     bulk_wait_read<0>();
@@ -162,6 +194,7 @@ __device__ __forceinline__ uint32_t quant4(uint32_t a, uint32_t b, float inv) {
 }
 
 // Shared image of one quantised row: H bytes, then H/128 scales (16-byte aligned).
+template <bool EP>
 __global__ void __launch_bounds__(kQThreads) scatter_bulk_fp8_kernel(const BulkArgs a) {
   extern __shared__ __align__(128) unsigned char smem[];
   pdl_sync();
@@ -171,8 +204,6 @@ __global__ void __launch_bounds__(kQThreads) scatter_bulk_fp8_kernel(const BulkA
   const uint32_t s_bytes = (uint32_t)nb * 4;
   const uint32_t img = (q_bytes + s_bytes + 127u) & ~127u;
   const uint4* x4 = reinterpret_cast<const uint4*>(a.x);
-  unsigned char* out_q = static_cast<unsigned char*>(a.rows);
-  unsigned char* out_s = reinterpret_cast<unsigned char*>(a.scales);
 
   int64_t i = 0;
   for (int64_t t = blockIdx.x; t < a.T; t += gridDim.x, ++i) {
@@ -211,8 +242,11 @@ __global__ void __launch_bounds__(kQThreads) scatter_bulk_fp8_kernel(const BulkA
     __syncthreads();
     if (tid < a.K) {
       if (pos >= 0) {
-        bulk_store(out_q + (size_t)pos * q_bytes, smem_u32(buf), q_bytes);
-        bulk_store(out_s + (size_t)pos * s_bytes, smem_u32(buf + q_bytes), s_bytes);
+        unsigned char *out_q, *out_s;
+        int64_t r;
+        bulk_dest<EP>(a, t, tid, pos, out_q, out_s, r);
+        bulk_store(out_q + (size_t)r * q_bytes, smem_u32(buf), q_bytes);
+        bulk_store(out_s + (size_t)r * s_bytes, smem_u32(buf + q_bytes), s_bytes);
       }
       bulk_commit();
     }
@@ -232,24 +266,17 @@ bool bulk_scatter_eligible(const moe_rd_params& p) {
 }
 
 cudaError_t init_bulk_attributes() {
-  cudaError_t e = cudaFuncSetAttribute(scatter_bulk_bf16_kernel,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+  const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+  cudaError_t e = cudaFuncSetAttribute(scatter_bulk_bf16_kernel<false>, attr, 200 * 1024);
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(scatter_bulk_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              200 * 1024);
+  e = cudaFuncSetAttribute(scatter_bulk_bf16_kernel<true>, attr, 200 * 1024);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(scatter_bulk_fp8_kernel<false>, attr, 200 * 1024);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(scatter_bulk_fp8_kernel<true>, attr, 200 * 1024);
 }
 
-cudaError_t launch_scatter_bulk(const moe_rd_params& p, const moe_rd_buffers& b, int32_t* status,
-                                cudaStream_t s) {
-  BulkArgs a;
-  a.x = static_cast<const uint16_t*>(b.x);
-  a.inverse_perm = b.inverse_perm;
-  a.rows = b.permuted;
-  a.scales = b.scales;
-  a.status = status;
-  a.T = p.T;
-  a.H = p.H;
-  a.K = p.K;
+static cudaError_t launch_bulk_args(const moe_rd_params& p, BulkArgs& a, bool ep, cudaStream_t s) {
   const int sms = device_sms();
   cudaError_t e;
   if (p.rows_format == MOE_RD_ROWS_FP8_E4M3_B128) {
@@ -261,7 +288,8 @@ cudaError_t launch_scatter_bulk(const moe_rd_params& p, const moe_rd_buffers& b,
     int64_t grid = (int64_t)sms * per_sm;
     if (grid > p.T) grid = p.T;
     a.stages = 2;
-    e = launch_pdl(scatter_bulk_fp8_kernel, dim3((unsigned)grid), dim3(kQThreads), smem, s, a);
+    e = ep ? launch_pdl(scatter_bulk_fp8_kernel<true>, dim3((unsigned)grid), dim3(kQThreads), smem, s, a)
+           : launch_pdl(scatter_bulk_fp8_kernel<false>, dim3((unsigned)grid), dim3(kQThreads), smem, s, a);
   } else {
     const size_t row = (size_t)p.H * 2;
     // about 160 KB of rows in flight per SM, at least 2 stages per warp
@@ -274,10 +302,48 @@ cudaError_t launch_scatter_bulk(const moe_rd_params& p, const moe_rd_buffers& b,
     int64_t grid = (int64_t)sms * per_sm;
     if (grid > p.T) grid = p.T;
     a.stages = stages;
-    e = launch_pdl(scatter_bulk_bf16_kernel, dim3((unsigned)grid), dim3(32), smem, s, a);
+    e = ep ? launch_pdl(scatter_bulk_bf16_kernel<true>, dim3((unsigned)grid), dim3(32), smem, s, a)
+           : launch_pdl(scatter_bulk_bf16_kernel<false>, dim3((unsigned)grid), dim3(32), smem, s, a);
   }
   count_launch();
   return e;
+}
+
+cudaError_t launch_scatter_bulk(const moe_rd_params& p, const moe_rd_buffers& b, int32_t* status,
+                                cudaStream_t s) {
+  BulkArgs a = {};
+  a.x = static_cast<const uint16_t*>(b.x);
+  a.inverse_perm = b.inverse_perm;
+  a.rows = b.permuted;
+  a.scales = b.scales;
+  a.status = status;
+  a.T = p.T;
+  a.H = p.H;
+  a.K = p.K;
+  return launch_bulk_args(p, a, false, s);
+}
+
+// Expert-parallel form: destinations are rows of the owners' buffers.
+cudaError_t launch_scatter_bulk_ep(const moe_rd_params& p, const void* x, const int32_t* ids,
+                                   const int32_t* inverse_perm, const int32_t* offsets,
+                                   const int32_t* dest_base, int world, void* const* peer_rows,
+                                   float* const* peer_scales, int32_t* status, cudaStream_t s) {
+  BulkArgs a = {};
+  a.x = static_cast<const uint16_t*>(x);
+  a.inverse_perm = inverse_perm;
+  a.status = status;
+  a.T = p.T;
+  a.H = p.H;
+  a.K = p.K;
+  a.ids = ids;
+  a.offsets = offsets;
+  a.dest_base = dest_base;
+  a.epr = p.E / world;
+  for (int d = 0; d < world; ++d) {
+    a.peer_rows[d] = peer_rows[d];
+    a.peer_scales[d] = peer_scales != nullptr ? peer_scales[d] : nullptr;
+  }
+  return launch_bulk_args(p, a, true, s);
 }
 
 }  // namespace moe_rd

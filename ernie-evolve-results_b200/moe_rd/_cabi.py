@@ -82,7 +82,7 @@ def lib() -> ctypes.CDLL:
         L.moe_rd_ep_scatter.argtypes = [ctypes.POINTER(Params), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                         ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int,
                                         ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
-                                        ctypes.c_void_p]
+                                        ctypes.c_void_p, ctypes.c_void_p]
         L.moe_rd_ep_scatter.restype = ctypes.c_int
         L.moe_rd_read_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         L.moe_rd_read_status.restype = ctypes.c_int

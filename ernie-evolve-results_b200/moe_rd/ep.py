@@ -125,8 +125,17 @@ class ExpertParallelFused:
     reads its buffer.
     """
 
-    def __init__(self, session, group=None, max_recv_rows: Optional[int] = None):
+    def __init__(self, session, group=None, max_recv_rows: Optional[int] = None,
+                 bulk: Optional[bool] = None):
         import torch.distributed._symmetric_memory as symm_mem
+        # Whole-row bulk copies (cp.async.bulk through shared memory) measured ~7 % more NVLink
+        # bandwidth than 16-byte stores; they need 16-byte aligned scale rows (H % 512 == 0).
+        H = session.H
+        img = (H + (H // 128) * 4 + 127) // 128 * 128
+        ok = (H % 512 == 0 and 2 * img <= 200 * 1024) if session.fp8 else (H * 4 + 64 <= 200 * 1024)
+        if bulk and not ok:
+            raise ValueError("bulk expert-parallel scatter is not available for this row size")
+        self.bulk = ok if bulk is None else bulk
         self.sess = session
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -174,8 +183,12 @@ class ExpertParallelFused:
         _cabi.check(L.moe_rd_ep_plan(ptr(self.kept_all), self.world, self.rank, self.sess.E, self.max_rows,
                                      ptr(self.dest_base), ptr(self.cnt), ptr(self.local_offsets), ptr(self.status),
                                      stream))
-        _cabi.check(L.moe_rd_ep_scatter(ctypes.byref(self.sess.params), ptr(x), ptr(r.expert_ids),
+        params = self.sess.params
+        if self.bulk:
+            params = _cabi.Params.from_buffer_copy(self.sess.params)
+            params.scatter_impl = _cabi.SCATTER_IMPL["bulk"]
+        _cabi.check(L.moe_rd_ep_scatter(ctypes.byref(params), ptr(x), ptr(r.expert_ids),
                                         ptr(r.inverse_perm), ptr(offs), ptr(self.dest_base), self.world,
-                                        self.peer_rows, self.peer_scales, stream))
+                                        self.peer_rows, self.peer_scales, ptr(self.status), stream))
         dist.all_reduce(self.token, group=self.group)  # every rank's stores are done and visible after this
         return EPResult(self.rows, self.scales, self.local_offsets, self.cnt, -1, -1)

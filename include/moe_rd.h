@@ -184,6 +184,8 @@ int moe_rd_ep_unpack(const int32_t* cnt, int world, int experts_per_rank, const 
  * `world` device pointers that this GPU can store to (peer-mapped memory; the
  * entry for `rank` is local).  Plain 16-byte stores; no multicast.  The caller
  * orders a cross-rank barrier after it before anyone reads the buffers.
+ * p->scatter_impl = MOE_RD_SCATTER_BULK moves whole rows with cp.async.bulk
+ * through shared memory instead (needs `status`, an 8-word device block).
  * Run the local pipeline with MOE_RD_SCATTER_NONE first.  No counterpart in the
  * reference (it has no expert parallelism).
  */
@@ -193,7 +195,7 @@ int moe_rd_ep_plan(const int32_t* kept_all, int world, int rank, int E, int64_t 
 int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const int32_t* expert_ids,
                       const int32_t* inverse_perm, const int32_t* offsets,
                       const int32_t* dest_base, int world, void* const* peer_rows,
-                      float* const* peer_scales, void* stream);
+                      float* const* peer_scales, int32_t* status, void* stream);
 
 /*
  * Same work as moe_rd_route_dispatch, but with a CUDA event recorded on

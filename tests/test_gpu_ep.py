@@ -40,12 +40,13 @@ def _worker(rank, world, port, T0, H, mode, q):
         E, K = 256, 8
         T = T0 + 64 * rank  # ragged: ranks hold different token counts
         t, kw = workloads.make("c5", T=T, H=H, rank=rank)
-        fused = mode == "fused"
+        fused = mode.startswith("fused")
         sess = Session(T, H, E, K, device=dev, score_fn="sigmoid", bias_mode="select", n_groups=8, topk_groups=4,
                        group_topk=2, routed_scale=2.5, rows_format="fp8", return_logits=True,
                        scatter_impl="none" if fused else "auto")
         cls = ExpertParallelFused if fused else ExpertParallel
-        ep = cls(sess, max_recv_rows=world * (T0 + 64 * world) * K)
+        kwargs = dict(bulk=True) if mode == "fused_bulk" else {}
+        ep = cls(sess, max_recv_rows=world * (T0 + 64 * world) * K, **kwargs)
         x, w, b = t["x"].to(dev), t["w"].to(dev), t["bias"].to(dev)
         for _ in range(2):  # twice: buffers are reused
             sess.run(x, w, b)
@@ -78,7 +79,7 @@ def _worker(rank, world, port, T0, H, mode, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-@pytest.mark.parametrize("mode", ["nccl", "fused"])
+@pytest.mark.parametrize("mode", ["nccl", "fused", "fused_bulk"])
 def test_expert_parallel_exchange_matches_oracle(mode):
     import torch.multiprocessing as mp
     world = min(torch.cuda.device_count(), 4)
