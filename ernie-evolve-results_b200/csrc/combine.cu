@@ -1,0 +1,176 @@
+// Weighted combine (un-permute): out[t,:] = shared[t,:] + sum_k w[t,k] * y[inverse_perm[t,k],:]
+//
+// The consumer of inverse_perm and combine_weights; follows combine_kernel of
+// the reference (kernel.cu:2365-2428): the K gathered 16-byte vectors are all
+// loaded before any arithmetic (so K loads are outstanding per lane), the fp32
+// accumulator starts from the shared-expert row (or 0), slots are added in
+// order k = 0..K-1 by one fused multiply-add each, the result is rounded once
+// to bf16; loads and stores carry streaming hints because every byte is touched
+// once (kernel.cu:2391-2404).  Pairs dropped by the capacity limit
+// (inverse_perm < 0) contribute nothing.  Work units (a token x 32 vectors of
+// 16 bytes) are dealt to warps grid-stride with many more blocks than fit, as
+// in the row scatter.
+#include "common.cuh"
+
+namespace moe_rd {
+namespace {
+
+constexpr int kCombineThreads = 256;
+constexpr int kCombineWarps = kCombineThreads / 32;
+constexpr int kCombineBlocksPerSm = 64;
+
+struct CombineArgs {
+  const uint4* y;
+  const int32_t* inverse_perm;
+  const float* weights;
+  const uint4* shared;
+  uint4* out;
+  int64_t T;
+  int nvec, K;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+template <int KT>
+__device__ __forceinline__ void combine_unit(const CombineArgs& a, int64_t t, int v) {
+  int pos[KT];
+  float w[KT];
+  uint4 yv[KT];
+#pragma unroll
+  for (int k = 0; k < KT; ++k) {
+    pos[k] = k < a.K ? __ldg(a.inverse_perm + (size_t)t * a.K + k) : -1;
+    w[k] = k < a.K ? __ldg(a.weights + (size_t)t * a.K + k) : 0.0f;
+  }
+#pragma unroll
+  for (int k = 0; k < KT; ++k)
+    if (pos[k] >= 0) yv[k] = __ldcs(a.y + (size_t)pos[k] * a.nvec + v);
+  float acc[8];
+  if (a.shared != nullptr) {
+    const uint4 s = __ldcs(a.shared + (size_t)t * a.nvec + v);
+    unpack8(s, acc);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+  }
+#pragma unroll
+  for (int k = 0; k < KT; ++k) {
+    if (pos[k] >= 0) {
+      float f[8];
+      unpack8(yv[k], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] = fmaf(w[k], f[j], acc[j]);
+    }
+  }
+  uint4 o;
+  o.x = pack_bf16x2(acc[0], acc[1]);
+  o.y = pack_bf16x2(acc[2], acc[3]);
+  o.z = pack_bf16x2(acc[4], acc[5]);
+  o.w = pack_bf16x2(acc[6], acc[7]);
+  __stcs(a.out + (size_t)t * a.nvec + v, o);
+}
+
+// K > 8: same arithmetic with the loads issued eight at a time.
+__device__ __forceinline__ void combine_unit_any(const CombineArgs& a, int64_t t, int v) {
+  float acc[8];
+  if (a.shared != nullptr) {
+    const uint4 s = __ldcs(a.shared + (size_t)t * a.nvec + v);
+    unpack8(s, acc);
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+  }
+  for (int k0 = 0; k0 < a.K; k0 += 8) {
+    int pos[8];
+    float w[8];
+    uint4 yv[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      pos[k] = k0 + k < a.K ? __ldg(a.inverse_perm + (size_t)t * a.K + k0 + k) : -1;
+      w[k] = k0 + k < a.K ? __ldg(a.weights + (size_t)t * a.K + k0 + k) : 0.0f;
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k)
+      if (pos[k] >= 0) yv[k] = __ldcs(a.y + (size_t)pos[k] * a.nvec + v);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      if (pos[k] >= 0) {
+        float f[8];
+        unpack8(yv[k], f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = fmaf(w[k], f[j], acc[j]);
+      }
+    }
+  }
+  uint4 o;
+  o.x = pack_bf16x2(acc[0], acc[1]);
+  o.y = pack_bf16x2(acc[2], acc[3]);
+  o.z = pack_bf16x2(acc[4], acc[5]);
+  o.w = pack_bf16x2(acc[6], acc[7]);
+  __stcs(a.out + (size_t)t * a.nvec + v, o);
+}
+
+template <int KT>
+__global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineArgs a) {
+  pdl_sync();
+  const int lane = threadIdx.x & 31;
+  const int upr = (a.nvec + 31) >> 5;  // units per row
+  const int64_t total = a.T * upr;
+  const int64_t W = (int64_t)gridDim.x * kCombineWarps;
+  for (int64_t u = (int64_t)blockIdx.x * kCombineWarps + (threadIdx.x >> 5); u < total; u += W) {
+    const int64_t t = u / upr;
+    const int v = (int)(u - t * upr) * 32 + lane;
+    if (v >= a.nvec) continue;
+    if (KT > 0)
+      combine_unit<(KT > 0 ? KT : 1)>(a, t, v);
+    else
+      combine_unit_any(a, t, v);
+  }
+}
+
+}  // namespace
+
+int device_sms();
+
+}  // namespace moe_rd
+
+using namespace moe_rd;
+
+extern "C" int moe_rd_combine(int64_t T, int32_t H, int32_t K, const void* y,
+                              const int32_t* inverse_perm, const float* combine_weights,
+                              const void* shared, void* out, void* stream) {
+  if (T < 0 || H < 8 || H % 8 != 0 || K < 1 || K > kMaxK) return MOE_RD_E_SHAPE;
+  if (T == 0) return MOE_RD_OK;
+  if (y == nullptr || inverse_perm == nullptr || combine_weights == nullptr || out == nullptr)
+    return MOE_RD_E_NULL;
+  if ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out) |
+       reinterpret_cast<uintptr_t>(shared)) & 15)
+    return MOE_RD_E_ALIGN;
+  CombineArgs a;
+  a.y = static_cast<const uint4*>(y);
+  a.inverse_perm = inverse_perm;
+  a.weights = combine_weights;
+  a.shared = static_cast<const uint4*>(shared);
+  a.out = static_cast<uint4*>(out);
+  a.T = T;
+  a.nvec = H / 8;
+  a.K = K;
+  const int64_t units = T * ((a.nvec + 31) / 32);
+  const int64_t want = (units + kCombineWarps - 1) / kCombineWarps;
+  const int64_t cap = (int64_t)device_sms() * kCombineBlocksPerSm;
+  const dim3 grid((unsigned)(want < cap ? want : cap));
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e;
+  if (K <= 2)
+    e = launch_pdl(combine_kernel<2>, grid, dim3(kCombineThreads), 0, s, a);
+  else if (K <= 4)
+    e = launch_pdl(combine_kernel<4>, grid, dim3(kCombineThreads), 0, s, a);
+  else if (K <= 8)
+    e = launch_pdl(combine_kernel<8>, grid, dim3(kCombineThreads), 0, s, a);
+  else
+    e = launch_pdl(combine_kernel<0>, grid, dim3(kCombineThreads), 0, s, a);
+  count_launch();
+  return e == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
+}

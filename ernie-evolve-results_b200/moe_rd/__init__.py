@@ -21,7 +21,7 @@ import torch
 from . import _cabi
 from ._cabi import MoeRdError  # noqa: F401
 
-__all__ = ["route_dispatch", "RouteDispatchResult", "MoeRdError", "capacity_from_factor"]
+__all__ = ["route_dispatch", "combine", "RouteDispatchResult", "MoeRdError", "capacity_from_factor"]
 
 
 class RouteDispatchResult(NamedTuple):
@@ -187,3 +187,35 @@ def route_dispatch(hidden_states: torch.Tensor, gate_weight: Optional[torch.Tens
         logits = None
     return RouteDispatchResult(permuted, offsets, inv, weights,
                                scales if rows_format == "fp8" else None, drop, ids, logits, counts)
+
+
+def _combine_impl(y, inverse_perm, combine_weights, shared):
+    if not y.is_cuda:
+        raise RuntimeError("moe_rd.combine has no CPU path")
+    if y.dtype != torch.bfloat16 or inverse_perm.dtype != torch.int32 or combine_weights.dtype != torch.float32:
+        raise TypeError("combine expects y bf16, inverse_perm int32, combine_weights float32")
+    y = y.contiguous()
+    inv = inverse_perm.contiguous()
+    w = combine_weights.contiguous()
+    T, K = inv.shape
+    H = y.shape[-1]
+    sh = None if shared is None else shared.reshape(T, H).contiguous()
+    with torch.cuda.device(y.device):
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=y.device)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(y.device).cuda_stream)
+        _cabi.check(_cabi.lib().moe_rd_combine(T, H, K, _ptr(y), _ptr(inv), _ptr(w), _ptr(sh), _ptr(out), stream))
+    return out
+
+
+_torch_lib.define("combine(Tensor y, Tensor inverse_perm, Tensor combine_weights, Tensor? shared) -> Tensor")
+_torch_lib.impl("combine", _combine_impl, "CUDA")
+
+
+def combine(y: torch.Tensor, inverse_perm: torch.Tensor, combine_weights: torch.Tensor,
+            shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = shared[t] + sum_k combine_weights[t,k] * y[inverse_perm[t,k]]  (bf16 in, bf16 out).
+
+    The inverse of ``route_dispatch``'s permutation with the routing weights
+    applied: ``y`` holds the expert outputs in expert-major row order.  Mirrors
+    the reference's combine_kernel (kernel.cu:2365-2428)."""
+    return torch.ops.moe_rd.combine(y, inverse_perm, combine_weights, shared)

@@ -198,6 +198,18 @@ int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const int32_t* expe
                       float* const* peer_scales, int32_t* status, void* stream);
 
 /*
+ * Weighted combine, the consumer of inverse_perm and combine_weights:
+ *   out[t,:] = shared[t,:] + sum_k combine_weights[t,k] * y[inverse_perm[t,k],:]
+ * y [rows,H] bf16 are the expert outputs in the permuted (expert-major) order,
+ * shared [T,H] bf16 may be NULL, out [T,H] bf16.  fp32 accumulation from the
+ * shared row, one fused multiply-add per slot in slot order, one rounding to
+ * bf16: the arithmetic of the reference's combine_kernel (kernel.cu:2365-2428).
+ * Dropped pairs (inverse_perm < 0) are skipped.
+ */
+int moe_rd_combine(int64_t T, int32_t H, int32_t K, const void* y, const int32_t* inverse_perm,
+                   const float* combine_weights, const void* shared, void* out, void* stream);
+
+/*
  * Same work as moe_rd_route_dispatch, but with a CUDA event recorded on
  * `stream` between the stages; synchronises the stream and returns the device
  * time of each stage in milliseconds: stage_ms[0] gate product, [1] scoring /

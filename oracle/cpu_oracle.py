@@ -67,6 +67,8 @@ def lib() -> ctypes.CDLL:
         L.moe_oracle_f32_to_e4m3.restype = ctypes.c_uint8
         L.moe_oracle_e4m3_to_f32.argtypes = [ctypes.c_uint8]
         L.moe_oracle_e4m3_to_f32.restype = f32
+        L.moe_oracle_combine.argtypes = [vp, vp, vp, vp, i64, i32, i32, vp]
+        L.moe_oracle_combine.restype = None
         L.moe_oracle_max_threads.restype = i32
         L.moe_oracle_set_threads.argtypes = [i32]
         _lib = L
@@ -192,6 +194,19 @@ def ep_exchange(per_rank, E, world):
         out.append({"rows": np.concatenate(rows, axis=0),
                     "scales": np.concatenate(scl, axis=0) if scl else None,
                     "counts": cnt, "offsets": offs})
+    return out
+
+
+def combine(y_u16, inverse_perm, weights, shared_u16=None):
+    """out[t] = shared[t] + sum_k w[t,k] * y[inverse_perm[t,k]] (bf16 bits in, bf16 bits out)."""
+    y = _c(y_u16, np.uint16)
+    inv = _c(inverse_perm, np.int32)
+    w = _c(weights, np.float32)
+    sh = _c(shared_u16, np.uint16)
+    T, K = inv.shape
+    H = y.shape[1]
+    out = np.empty((T, H), np.uint16)
+    lib().moe_oracle_combine(_p(y), _p(inv), _p(w), _p(sh), T, K, H, _p(out))
     return out
 
 

@@ -387,6 +387,39 @@ void moe_oracle_permute_fp8(const uint16_t* x, const int32_t* inverse_perm,
   }
 }
 
+/* float -> bf16, round to nearest even (finite inputs). */
+static inline uint16_t f32_to_bf16_rne(float f) {
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40); /* NaN */
+  u += 0x7fffu + ((u >> 16) & 1u);
+  return (uint16_t)(u >> 16);
+}
+
+/* ------------------------------------------------------------------------
+ * Weighted combine (un-permute): out[t,:] = shared[t,:] + sum_k w[t,k] * y[inverse_perm[t,k],:]
+ * Follows combine_kernel (kernel.cu:2365-2428): fp32 accumulator starting from
+ * the shared-expert row (or 0), slots added in order k = 0..K-1 by one fused
+ * multiply-add each (the reference's `acc += w * y` contracts to an FMA under
+ * nvcc's default -fmad=true), rounded once to bf16 at the end.  Dropped pairs
+ * (inverse_perm < 0) contribute nothing.
+ * ---------------------------------------------------------------------- */
+void moe_oracle_combine(const uint16_t* y, const int32_t* inverse_perm, const float* weights,
+                        const uint16_t* shared, int64_t T, int K, int H, uint16_t* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t t = 0; t < T; ++t) {
+    for (int h = 0; h < H; ++h) {
+      float acc = shared ? bf16_to_f32(shared[(size_t)t * H + h]) : 0.0f;
+      for (int k = 0; k < K; ++k) {
+        const int32_t pos = inverse_perm[(size_t)t * K + k];
+        if (pos < 0) continue;
+        acc = fmaf(weights[(size_t)t * K + k], bf16_to_f32(y[(size_t)pos * H + h]), acc);
+      }
+      out[(size_t)t * H + h] = f32_to_bf16_rne(acc);
+    }
+  }
+}
+
 int moe_oracle_max_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

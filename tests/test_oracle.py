@@ -299,3 +299,24 @@ def test_golden_fixture(name):
     assert _digest(r["permuted"]) == meta["permuted_sha256"]
     if r["scales"] is not None:
         assert _digest(r["scales"]) == meta["scales_sha256"]
+
+
+def test_combine_matches_numpy_restatement():
+    g = torch.Generator().manual_seed(21)
+    T, K, H, R = 40, 3, 64, 100
+    y = torch.randn(R, H, generator=g).to(torch.bfloat16)
+    sh = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    rng = np.random.default_rng(3)
+    inv = rng.integers(-1, R, size=(T, K)).astype(np.int32)
+    w = rng.random((T, K)).astype(np.float32)
+    yb, sb = _util.bf16_bits(y), _util.bf16_bits(sh)
+    for shared in (None, sb):
+        got = cpu_oracle.combine(yb, inv, w, shared)
+        yf = y.float().numpy().astype(np.float64)
+        acc = (sh.float().numpy() if shared is not None else np.zeros((T, H), np.float32)).astype(np.float32)
+        for k in range(K):
+            sel = inv[:, k] >= 0
+            prod = w[sel, k].astype(np.float64)[:, None] * yf[inv[sel, k]]
+            acc[sel] = (prod + acc[sel].astype(np.float64)).astype(np.float32)  # one fused multiply-add
+        ref = torch.from_numpy(acc).to(torch.bfloat16)
+        np.testing.assert_array_equal(got, _util.bf16_bits(ref))
