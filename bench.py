@@ -415,6 +415,47 @@ def run_ours(args, rank, world, local_rank):
         print(json.dumps(line), flush=True)
 
 
+def run_combine(args):
+    """`--op combine`: the weighted combine on the workload's shapes (one GPU), same timing rules."""
+    import torch
+    import moe_rd
+    from moe_rd import workloads
+    spec = workloads.SPECS[args.workload]
+    T, H, K = spec["T"], spec["H"], spec["K"]
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device="cpu").manual_seed(7)
+    R = T * K
+    y = torch.randn(R, H, generator=g, dtype=torch.float32).to(torch.bfloat16).to(dev)
+    sh = torch.randn(T, H, generator=g, dtype=torch.float32).to(torch.bfloat16).to(dev)
+    inv = torch.randperm(R, generator=g).to(torch.int32).view(T, K).to(dev)
+    w = torch.rand(T, K, generator=g).to(dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        moe_rd.combine(y, inv, w, sh)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    for s_, e_ in ev:
+        flush.zero_()
+        s_.record()
+        moe_rd.combine(y, inv, w, sh)
+        e_.record()
+    torch.cuda.synchronize()
+    ms = sum(s_.elapsed_time(e_) for s_, e_ in ev) / args.steps
+    nbytes = R * H * 2 + 2 * T * H * 2 + T * K * 8
+    peak, kind = measured_hbm_peak()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "combined_tokens_per_s", "value": T / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+        "config": {"workload": args.workload + " combine", "tokens": T, "hidden": H, "top_k": K,
+                   "l2": "flushed by a 256 MiB device write between steps"},
+        "roofline": {"bound": "hbm", "kernel": "combine_kernel", "achieved": gbs, "peak": peak, "unit": "GB/s",
+                     "frac": gbs / peak, "peak_kind": f"{kind} HBM copy bandwidth", "traffic": None,
+                     "bytes_per_launch": nbytes, "kernel_ms": ms},
+        "gpu_launches": args.steps}), flush=True)
+
+
 def main():
     # NCCL prints its version banner on stdout at this level; stdout carries the one JSON line
     if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
@@ -426,12 +467,17 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--scatter", default="auto", choices=["auto", "simt", "bulk"])
+    ap.add_argument("--op", default="route_dispatch", choices=["route_dispatch", "combine"])
     ap.add_argument("--ep", default="fused", choices=["fused", "nccl"],
                     help="expert-parallel exchange at N > 1: one peer-store kernel, or NCCL all-to-all + reorder")
     args = ap.parse_args()
     rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if world == 1 and args.gpus > 1:
         raise SystemExit("launch with torchrun for --gpus > 1 (one process per GPU)")
+    if args.op == "combine":
+        if rank == 0:
+            run_combine(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
     else:
