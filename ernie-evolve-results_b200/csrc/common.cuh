@@ -68,7 +68,7 @@ cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const P
                         int32_t* tile_base, int32_t* counts, int32_t* ticket, cudaStream_t s);
 cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                            const int32_t* ids, const int32_t* tile_base, int32_t* status,
-                           cudaStream_t s);
+                           cudaStream_t s, cudaEvent_t after_positions = nullptr);
 bool umma_available();
 bool gemv_eligible(const moe_rd_params& p);
 void count_launch(int n = 1);

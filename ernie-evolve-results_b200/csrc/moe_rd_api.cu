@@ -255,8 +255,8 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[2], s));
   MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, ticket, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[3], s));
-  MOE_RD_CUDA(launch_scatter(*p, *b, plan, ids, tile_base, status, s));
-  if (ev) MOE_RD_CUDA(cudaEventRecord(ev[4], s));
+  MOE_RD_CUDA(launch_scatter(*p, *b, plan, ids, tile_base, status, s, ev ? ev[4] : nullptr));
+  if (ev) MOE_RD_CUDA(cudaEventRecord(ev[5], s));
   return MOE_RD_OK;
 }
 
@@ -266,11 +266,11 @@ int moe_rd_route_dispatch(const moe_rd_params* p, const moe_rd_buffers* b, void*
 }
 
 int moe_rd_route_dispatch_timed(const moe_rd_params* p, const moe_rd_buffers* b, void* workspace,
-                                size_t workspace_bytes, void* stream, float stage_ms[4]) {
+                                size_t workspace_bytes, void* stream, float stage_ms[5]) {
   if (stage_ms == nullptr) return MOE_RD_E_NULL;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  cudaEvent_t ev[5] = {};
-  for (int i = 0; i < 5; ++i) {
+  cudaEvent_t ev[6] = {};
+  for (int i = 0; i < 6; ++i) {
     cudaError_t e = cudaEventCreate(&ev[i]);
     if (e != cudaSuccess) {
       for (int j = 0; j < i; ++j) cudaEventDestroy(ev[j]);
@@ -281,14 +281,14 @@ int moe_rd_route_dispatch_timed(const moe_rd_params* p, const moe_rd_buffers* b,
   int rc = run_pipeline(p, b, workspace, workspace_bytes, s, ev);
   if (rc == MOE_RD_OK) {
     cudaError_t e = cudaStreamSynchronize(s);
-    for (int i = 0; i < 4 && e == cudaSuccess; ++i)
+    for (int i = 0; i < 5 && e == cudaSuccess; ++i)
       e = cudaEventElapsedTime(&stage_ms[i], ev[i], ev[i + 1]);
     if (e != cudaSuccess) {
       t_last_cuda = e;
       rc = MOE_RD_E_CUDA;
     }
   }
-  for (int i = 0; i < 5; ++i) cudaEventDestroy(ev[i]);
+  for (int i = 0; i < 6; ++i) cudaEventDestroy(ev[i]);
   return rc;
 }
 

@@ -336,8 +336,10 @@ cudaError_t init_scatter_attributes() {
 
 cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                            const int32_t* ids, const int32_t* tile_base, int32_t* status,
-                           cudaStream_t s) {
-  if (p.T == 0) return cudaSuccess;
+                           cudaStream_t s, cudaEvent_t after_positions) {
+  if (p.T == 0) {
+    return after_positions ? cudaEventRecord(after_positions, s) : cudaSuccess;
+  }
   PositionArgs pa;
   pa.ids = ids;
   pa.tile_base = tile_base;
@@ -355,6 +357,10 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
                              positions_smem(p.K, p.E), s, pa);
   count_launch();
   if (e != cudaSuccess) return e;
+  if (after_positions) {
+    e = cudaEventRecord(after_positions, s);
+    if (e != cudaSuccess) return e;
+  }
   if (plan.scatter == MOE_RD_SCATTER_NONE) return cudaSuccess;
   if (plan.scatter == MOE_RD_SCATTER_BULK) return launch_scatter_bulk(p, b, status, s);
 

@@ -80,10 +80,10 @@ class Session:
         return self.result()
 
     def run_timed(self, x, w, bias=None):
-        """One pass with per-stage device times in ms: (gate, route, scan, scatter). Synchronises."""
+        """One pass with per-stage device times in ms: (gate, route, scan, positions, scatter). Synchronises."""
         self._check_inputs(x, w)
         b = self._buffers(x, w, bias)
-        ms = (ctypes.c_float * 4)()
+        ms = (ctypes.c_float * 5)()
         stream = ctypes.c_void_p(torch.cuda.current_stream(self.device).cuda_stream)
         _cabi.check(_cabi.lib().moe_rd_route_dispatch_timed(
             ctypes.byref(self.params), ctypes.byref(b), ctypes.c_void_p(self.workspace.data_ptr()),

@@ -213,13 +213,14 @@ int moe_rd_combine(int64_t T, int32_t H, int32_t K, const void* y, const int32_t
  * Same work as moe_rd_route_dispatch, but with a CUDA event recorded on
  * `stream` between the stages; synchronises the stream and returns the device
  * time of each stage in milliseconds: stage_ms[0] gate product, [1] scoring /
- * top-k / tile histogram, [2] scans, [3] row scatter.  For measurement only
+ * top-k / expert histogram (with the fused GEMV gate the product is in here),
+ * [2] scans, [3] positions, [4] row scatter.  For measurement only
  * (the reference's per-kernel figures come from an external profiler,
  * kernel.cu:865-890); it creates and destroys events, so keep it off hot paths.
  */
 int moe_rd_route_dispatch_timed(const moe_rd_params* p, const moe_rd_buffers* b,
                                 void* workspace, size_t workspace_bytes, void* stream,
-                                float stage_ms[4]);
+                                float stage_ms[5]);
 
 /*
  * Copies the 8-word device status block of the last call that used
