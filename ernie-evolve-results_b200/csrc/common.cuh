@@ -133,6 +133,7 @@ __device__ __forceinline__ float exp_ieee(float x) {
   if (x < -87.0f) return 0.0f;
   if (x > 88.0f) return __int_as_float(0x7f800000);
   const float n = rintf(__fmul_rn(x, 1.44269504f));
+  const int ni = (int)n;
   float r = fmaf(n, -0.693145752f, x);
   r = fmaf(n, -1.42860677e-6f, r);
   float p = 1.9875691500e-4f;
@@ -144,7 +145,7 @@ __device__ __forceinline__ float exp_ieee(float x) {
   const float r2 = __fmul_rn(r, r);
   float y = fmaf(p, r2, r);
   y = __fadd_rn(y, 1.0f);
-  const float s = __int_as_float(((int)n + 127) << 23);
+  const float s = __int_as_float((ni + 127) << 23);
   return __fmul_rn(y, s);
 }
 

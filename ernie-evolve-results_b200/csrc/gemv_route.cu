@@ -224,7 +224,7 @@ gemv_route_kernel(const GemvArgs g, const RouteArgs a) {
         float z[1] = {mine};
         int mysel;
         float myw;
-        route_token<1>(a, z, lane, mysel, myw);
+        route_token<1, false>(a, z, lane, nullptr, mysel, myw);
         publish_token(a, t, lane, mysel, myw, s_cnt);
       }
     }

@@ -7,40 +7,57 @@
 namespace moe_rd {
 namespace {
 
+#ifndef MOE_RD_ROUTE_PREFETCH
+#define MOE_RD_ROUTE_PREFETCH 1
+#endif
 constexpr int kRouteThreads = 512;
 constexpr int kRouteWarps = kRouteThreads / 32;
 
 // One warp per token.  Block b owns the contiguous token range
 // [T*b/B, T*(b+1)/B): with B a multiple of the SM count every SM gets the same
-// number of tokens to within one, whatever T is.
-template <int EPL>
-__global__ void __launch_bounds__(kRouteThreads) route_kernel(const RouteArgs a) {
+// number of tokens to within one, whatever T is.  The logits of a warp's next
+// token are requested before the current one is scored.  MB = resident blocks
+// per SM the register budget is cut for: 3 pays when every warp has several
+// tokens to work through, 2 when it has one or two.
+template <int EPL, bool FULL>
+__device__ __forceinline__ void load_logits(const RouteArgs& a, int64_t t, int lane, float (&z)[EPL]) {
+  const size_t row = (size_t)t * a.E;
+#pragma unroll
+  for (int i = 0; i < EPL; ++i) {
+    const int e = lane + 32 * i;
+    float v = 0.0f;
+    if (FULL || e < a.E) {
+      v = __ldg(a.logits + row + e);
+      for (int sp = 1; sp < a.nsplit; ++sp)
+        v = __fadd_rn(v, __ldg(a.logits + (size_t)sp * a.T * a.E + row + e));
+      if (a.logit_bias != nullptr) v = __fadd_rn(v, __ldg(a.logit_bias + e));
+      if (a.logits_out != nullptr) a.logits_out[row + e] = v;
+    }
+    z[i] = v;
+  }
+}
+
+template <int EPL, bool FULL, int MB>
+__global__ void __launch_bounds__(kRouteThreads, MB) route_kernel(const RouteArgs a) {
   __shared__ int s_cnt[kMaxE];
+  __shared__ float s_sc[EPL > 1 ? kRouteWarps * 32 * EPL : 1];
   for (int e = threadIdx.x; e < a.E; e += kRouteThreads) s_cnt[e] = 0;
   __syncthreads();
   pdl_sync();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int64_t lo = a.T * blockIdx.x / gridDim.x;
   const int64_t hi = a.T * (blockIdx.x + 1) / gridDim.x;
+  float zn[EPL];
+  if (lo + warp < hi) load_logits<EPL, FULL>(a, lo + warp, lane, zn);
   for (int64_t t = lo + warp; t < hi; t += kRouteWarps) {
-    const size_t row = (size_t)t * a.E;
     float z[EPL];
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      const int e = lane + 32 * i;
-      float v = 0.0f;
-      if (e < a.E) {
-        v = __ldg(a.logits + row + e);
-        for (int sp = 1; sp < a.nsplit; ++sp)
-          v = __fadd_rn(v, __ldg(a.logits + (size_t)sp * a.T * a.E + row + e));
-        if (a.logit_bias != nullptr) v = __fadd_rn(v, __ldg(a.logit_bias + e));
-        if (a.logits_out != nullptr) a.logits_out[row + e] = v;
-      }
-      z[i] = v;
-    }
+    for (int i = 0; i < EPL; ++i) z[i] = zn[i];
+    if (!MOE_RD_ROUTE_PREFETCH && t > lo + warp) load_logits<EPL, FULL>(a, t, lane, z);
+    if (MOE_RD_ROUTE_PREFETCH && t + kRouteWarps < hi) load_logits<EPL, FULL>(a, t + kRouteWarps, lane, zn);
     int mysel;
     float myw;
-    route_token<EPL>(a, z, lane, mysel, myw);
+    route_token<EPL, FULL>(a, z, lane, EPL > 1 ? s_sc + warp * 32 * EPL : nullptr, mysel, myw);
     publish_token(a, t, lane, mysel, myw, s_cnt);
   }
   __syncthreads();
@@ -174,20 +191,34 @@ cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b,
   a.nsplit = nsplit;
   a.logit_bias = logit_bias;
   a.logits_out = logits_out;
-  // two resident blocks of 512 threads per SM (<= 64 registers per thread)
-  int64_t nblk = (int64_t)device_sms() * 2;
+  // Three resident blocks of 512 threads per SM when every warp then still has
+  // at least two tokens and 40 registers hold a token (<= 4 experts per lane),
+  // else two.
+  const int sms = device_sms();
+  const int epl = p.E <= 32 ? 1 : p.E <= 64 ? 2 : p.E <= 128 ? 4 : 8;
+  const bool three = epl <= 4 && p.T >= (int64_t)sms * 3 * kRouteWarps * 2;
+  int64_t nblk = (int64_t)sms * (three ? 3 : 2);
   const int64_t need = (p.T + kRouteWarps - 1) / kRouteWarps;
   if (nblk > need) nblk = need;
   const dim3 grid((unsigned)nblk);
+  const dim3 blk(kRouteThreads);
+  const bool full = p.E == 32 * epl;
   cudaError_t e;
-  if (p.E <= 32)
-    e = launch_pdl(route_kernel<1>, grid, dim3(kRouteThreads), 0, s, a);
-  else if (p.E <= 64)
-    e = launch_pdl(route_kernel<2>, grid, dim3(kRouteThreads), 0, s, a);
-  else if (p.E <= 128)
-    e = launch_pdl(route_kernel<4>, grid, dim3(kRouteThreads), 0, s, a);
-  else
-    e = launch_pdl(route_kernel<8>, grid, dim3(kRouteThreads), 0, s, a);
+#define MOE_RD_ROUTE_CASE(EPL_)                                                              \
+  case EPL_:                                                                                 \
+    e = full ? (three ? launch_pdl(route_kernel<EPL_, true, 3>, grid, blk, 0, s, a)          \
+                      : launch_pdl(route_kernel<EPL_, true, 2>, grid, blk, 0, s, a))         \
+             : (three ? launch_pdl(route_kernel<EPL_, false, 3>, grid, blk, 0, s, a)         \
+                      : launch_pdl(route_kernel<EPL_, false, 2>, grid, blk, 0, s, a));       \
+    break;
+  switch (epl) {
+    MOE_RD_ROUTE_CASE(1)
+    MOE_RD_ROUTE_CASE(2)
+    MOE_RD_ROUTE_CASE(4)
+    default:
+    MOE_RD_ROUTE_CASE(8)
+  }
+#undef MOE_RD_ROUTE_CASE
   count_launch();
   return e;
 }

@@ -22,6 +22,10 @@
 
 #include "common.cuh"
 
+#ifndef MOE_RD_ROUTE_SORTED
+#define MOE_RD_ROUTE_SORTED 1
+#endif
+
 namespace moe_rd {
 
 struct RouteArgs {
@@ -55,21 +59,28 @@ __device__ __forceinline__ float ord_value(uint32_t k) {
 // Scores one token held as z[i] = logit of expert lane + 32*i and selects its
 // K experts.  On return lane k < K holds slot k: `mysel` the expert, `myw` the
 // combine weight.  All 32 lanes of the warp must call.
-template <int EPL>
+//
+// FULL: E == 32*EPL, so no register needs a bounds test.  s_sc: null, or 32*EPL
+// floats of shared memory owned by this warp; the scores are then parked there
+// and lane k fetches the score of its expert after the selection, instead of
+// every round broadcasting it out of a register picked by a chain of selects.
+// A selected key is removed by zeroing its image (0 = not eligible), so a round
+// costs one max pass, one index pass and one removal pass over the registers.
+template <int EPL, bool FULL>
 __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)[EPL], int lane,
-                                            int& mysel, float& myw) {
+                                            float* s_sc, int& mysel, float& myw) {
   float sc[EPL];
   uint32_t ok[EPL];  // ordered images of the selection keys; 0 = not eligible
   if (a.score_fn == MOE_RD_SCORE_SOFTMAX) {
     uint32_t mk = 0u;
 #pragma unroll
     for (int i = 0; i < EPL; ++i)
-      if (lane + 32 * i < a.E) mk = max(mk, ord_key(z[i]));
+      if (FULL || lane + 32 * i < a.E) mk = max(mk, ord_key(z[i]));
     const float m = ord_value(__reduce_max_sync(kFull, mk));
     float part = 0.0f;
 #pragma unroll
     for (int i = 0; i < EPL; ++i) {
-      const float p = lane + 32 * i < a.E ? exp_ieee(__fsub_rn(z[i], m)) : 0.0f;
+      const float p = (FULL || lane + 32 * i < a.E) ? exp_ieee(__fsub_rn(z[i], m)) : 0.0f;
       sc[i] = p;
       part = __fadd_rn(part, p);
     }
@@ -79,14 +90,20 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)
   } else {
 #pragma unroll
     for (int i = 0; i < EPL; ++i)
-      sc[i] = lane + 32 * i < a.E ? __frcp_rn(__fadd_rn(1.0f, exp_ieee(-z[i]))) : 0.0f;
+      sc[i] = (FULL || lane + 32 * i < a.E) ? __frcp_rn(__fadd_rn(1.0f, exp_ieee(-z[i]))) : 0.0f;
   }
 #pragma unroll
   for (int i = 0; i < EPL; ++i) {
     const int e = lane + 32 * i;
     float key = sc[i];
-    if (e < a.E && a.select_bias != nullptr) key = __fadd_rn(key, __ldg(a.select_bias + e));
-    ok[i] = e < a.E ? ord_key(key) : 0u;
+    if ((FULL || e < a.E) && a.select_bias != nullptr) key = __fadd_rn(key, __ldg(a.select_bias + e));
+    ok[i] = (FULL || e < a.E) ? ord_key(key) : 0u;
+  }
+  const bool staged = s_sc != nullptr && EPL > 1 && !a.weight_from_key;
+  if (staged) {
+    __syncwarp();  // the previous token's readers are done with s_sc
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) s_sc[lane + 32 * i] = sc[i];
   }
 
   if (a.n_groups > 1) {
@@ -168,45 +185,110 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)
       if (og > mygs || (og == mygs && o < lane)) ++rank;
     }
     const unsigned keep = __ballot_sync(kFull, lane < a.n_groups && rank < a.topk_groups);
+    if ((gs & 31) == 0) {
+      // register i belongs to group i / (gs/32), the same for every lane
+      const int m = gs >> 5;
+      int g = 0, c = 0;
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      const int e = lane + 32 * i;
-      if (e < a.E && !((keep >> (e / gs)) & 1u)) ok[i] = 0u;
+      for (int i = 0; i < EPL; ++i) {
+        if (!((keep >> g) & 1u)) ok[i] = 0u;
+        if (++c == m) {
+          c = 0;
+          ++g;
+        }
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        const int e = lane + 32 * i;
+        if (e < a.E && !((keep >> (e / gs)) & 1u)) ok[i] = 0u;
+      }
     }
   }
 
-  unsigned taken = 0;
   float tot = 0.0f, myu = 0.0f;
   mysel = 0;
-  for (int k = 0; k < a.K; ++k) {
-    uint32_t bk = 0u;
-    int bi = 0x7fffffff;
+  // With many registers per lane and many rounds it pays to sort each lane's
+  // keys once (descending; odd-even transposition with a strict compare keeps
+  // equal keys in index order) and then only look at the head of every lane.
+  const bool sorted = MOE_RD_ROUTE_SORTED && EPL >= 4 && (staged || a.weight_from_key) && a.K >= (EPL >= 8 ? 6 : 3);
+  if (sorted) {
+    int ix[EPL];
 #pragma unroll
-    for (int i = 0; i < EPL; ++i) {
-      if (!((taken >> i) & 1u) && ok[i] > bk) {  // strict: the lowest register wins ties
-        bk = ok[i];
-        bi = lane + 32 * i;
+    for (int i = 0; i < EPL; ++i) ix[i] = lane + 32 * i;
+#pragma unroll
+    for (int pass = 0; pass < EPL; ++pass) {
+#pragma unroll
+      for (int i = pass & 1; i + 1 < EPL; i += 2) {
+        const bool sw = ok[i + 1] > ok[i];
+        const uint32_t ka = ok[i], kb = ok[i + 1];
+        const int ia = ix[i], ib = ix[i + 1];
+        ok[i] = sw ? kb : ka;
+        ok[i + 1] = sw ? ka : kb;
+        ix[i] = sw ? ib : ia;
+        ix[i + 1] = sw ? ia : ib;
       }
     }
+    for (int k = 0; k < a.K; ++k) {
+      const uint32_t mx = __reduce_max_sync(kFull, ok[0]);
+      int win = (int)__reduce_min_sync(kFull, (unsigned)(ok[0] == mx ? ix[0] : 0x7fffffff));
+      if (mx == 0u) win = 0x7fffffff;   // nothing eligible is left
+      win = min(max(win, 0), a.E - 1);  // only then is the index out of range
+      const bool pop = ix[0] == win;
+#pragma unroll
+      for (int i = 0; i + 1 < EPL; ++i) {
+        ok[i] = pop ? ok[i + 1] : ok[i];
+        ix[i] = pop ? ix[i + 1] : ix[i];
+      }
+      if (pop) ok[EPL - 1] = 0u;
+      if (a.weight_from_key) {
+        const float cand = ord_value(mx);
+        tot = __fadd_rn(tot, cand);
+        if (lane == k) myu = cand;
+      }
+      if (lane == k) mysel = win;
+    }
+  } else {
+  for (int k = 0; k < a.K; ++k) {
+    uint32_t bk = ok[0];
+#pragma unroll
+    for (int i = 1; i < EPL; ++i) bk = max(bk, ok[i]);
     const uint32_t mx = __reduce_max_sync(kFull, bk);
-    int win = (int)__reduce_min_sync(kFull, (unsigned)(bk == mx ? bi : 0x7fffffff));
-    win = min(max(win, 0), a.E - 1);  // only non-finite inputs can get here out of range
-    const int oi = win >> 5, ol = win & 31;
-    float cand = 0.0f;
-    if (a.weight_from_key) {
-      cand = ord_value(mx);
-    } else {
+    int bi = 0x7fffffff;
+#pragma unroll
+    for (int i = EPL - 1; i >= 0; --i)
+      if (ok[i] == mx) bi = lane + 32 * i;  // descending: the lowest register wins ties
+    int win = (int)__reduce_min_sync(kFull, (unsigned)bi);
+    if (mx == 0u) win = 0x7fffffff;          // nothing eligible is left
+    win = min(max(win, 0), a.E - 1);         // only then is the index out of range
+    const int d = win - lane;                // == 32*i on the lane and register that hold it
+    if (staged) {
 #pragma unroll
       for (int i = 0; i < EPL; ++i)
-        if (i == oi) cand = sc[i];
-      cand = __shfl_sync(kFull, cand, ol);
+        if (d == 32 * i) ok[i] = 0u;
+      if (lane == k) mysel = win;
+    } else {
+      float cand = 0.0f;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        if (d == 32 * i) {
+          cand = sc[i];
+          ok[i] = 0u;
+        }
+      }
+      cand = a.weight_from_key ? ord_value(mx) : __shfl_sync(kFull, cand, win & 31);
+      tot = __fadd_rn(tot, cand);
+      if (lane == k) {
+        mysel = win;
+        myu = cand;
+      }
     }
-    if (ol == lane) taken |= 1u << oi;
-    tot = __fadd_rn(tot, cand);
-    if (lane == k) {
-      mysel = win;
-      myu = cand;
-    }
+  }
+  }
+  if (staged) {
+    __syncwarp();
+    if (lane < a.K) myu = s_sc[mysel];
+    for (int k = 0; k < a.K; ++k) tot = __fadd_rn(tot, __shfl_sync(kFull, myu, k));
   }
   const float wv = a.renorm ? __fdiv_rn(myu, fmaxf(tot, a.norm_min)) : myu;
   myw = __fmul_rn(wv, a.routed_scale);
