@@ -52,7 +52,7 @@ void carve(const moe_rd_params& p, const Plan& plan, bool need_logits, bool need
 cudaError_t launch_gate_simt(const moe_rd_params& p, const moe_rd_buffers& b, float* logits,
                              cudaStream_t s);
 cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                             void* wt, float* partial, float* logits, int32_t* status,
+                             void* wt, float* partial, float* logits, int32_t* status, void* zero, size_t zero_bytes,
                              cudaStream_t s);
 cudaError_t launch_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                          const float* logits, int32_t* ids, int32_t* tile_base, int32_t* counts,

@@ -117,6 +117,13 @@ __device__ __forceinline__ void umma_commit(uint32_t bar) {
                : "memory");
 }
 
+__device__ __forceinline__ void bulk_store_row(void* dst, uint32_t src_smem, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
+               "r"(src_smem), "r"(bytes)
+               : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+
 struct UmmaArgs {
   float* partial;  // [ksplit][T][E]
   int32_t* status;
@@ -124,6 +131,8 @@ struct UmmaArgs {
   int E, kblocks, ksplit, stages, tmem_cols;
   int w_mn_major;  // 1: map_w is over W[H,E] and B tiles are MN-major; 0: over W^T[E,H], K-major
   int mh;          // 128-token halves per CTA (1 or 2): two halves share every W tile
+  uint4* zero;     // region the epilogue warps clear while the first tiles load (or null)
+  uint32_t zero_vecs;
 };
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -174,6 +183,8 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
       int issued = 0;
       for (int i = 0; i < nkb; ++i) {
         const int s = i % a.stages;
@@ -246,6 +257,13 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
   } else {
     // epilogue: TMEM lane = token row of the tile
     const int q = warp & 3;
+    if (a.zero != nullptr) {
+      // Clear the counters of the later kernels while the first tiles are on
+      // their way (the routing kernel starts after this grid has finished).
+      const uint32_t nthr = gridDim.x * gridDim.y * 128u;
+      const uint32_t me = (blockIdx.y * gridDim.x + blockIdx.x) * 128u + (uint32_t)(q * 32 + lane);
+      for (uint32_t i = me; i < a.zero_vecs; i += nthr) a.zero[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
     bool ok = mbar_wait(smem_u32(accum_bar), 0u, abort_flag);
     ok = __all_sync(kFull, ok);
     if (!ok) {
@@ -253,50 +271,55 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       *abort_flag = 1;
     } else {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // All MMAs have completed, so the operand ring is free: every thread parks
+      // its token row there (row pitch E*4 + 16 bytes keeps the 16-byte stores of
+      // a warp on different banks) and sends it to memory with one bulk copy.
+      const uint32_t pitch = (uint32_t)a.E * 4u + 16u;
+      unsigned char* my_row = smem + (size_t)(q * 32 + lane) * pitch;
       for (int h = 0; h < a.mh; ++h) {
-      const int64_t row = ((int64_t)mt * a.mh + h) * kBlockM + q * 32 + lane;
-      float* out = a.partial + ((size_t)ks * a.T + (row < a.T ? row : 0)) * a.E;
-      for (int c = 0; c < a.E; c += 32) {
-        uint32_t r[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * a.E + c);
-        if (a.E - c >= 32) {
-          asm volatile(
-              "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-              "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-              "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-                "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-                "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-                "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-                "=r"(r[31])
-              : "r"(taddr)
-              : "memory");
-        } else {
-          // E % 32 == 16: the last 16 columns
+        const int64_t row = ((int64_t)mt * a.mh + h) * kBlockM + q * 32 + lane;
+        if (h > 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        for (int c = 0; c < a.E; c += 32) {
+          uint32_t r[32];
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * a.E + c);
+          if (a.E - c >= 32) {
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                  "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+                  "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                  "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                  "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+                  "=r"(r[31])
+                : "r"(taddr)
+                : "memory");
+          } else {
+            // E % 32 == 16: the last 16 columns
 #pragma unroll
-          for (int i = 16; i < 32; ++i) r[i] = 0u;
-          asm volatile(
-              "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-              "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-              : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-                "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-              : "r"(taddr)
-              : "memory");
-        }
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < a.T) {
+            for (int i = 16; i < 32; ++i) r[i] = 0u;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                  "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+                  "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                : "r"(taddr)
+                : "memory");
+          }
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
           const int n = a.E - c >= 32 ? 32 : 16;
-          float4* o4 = reinterpret_cast<float4*>(out + c);
+          uint4* o4 = reinterpret_cast<uint4*>(my_row + (size_t)c * 4);
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            if (4 * i < n)
-              o4[i] = make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                  __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+            if (4 * i < n) o4[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
         }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (row < a.T)
+          bulk_store_row(a.partial + ((size_t)ks * a.T + row) * a.E, smem_u32(my_row), (uint32_t)a.E * 4u);
       }
-      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
     }
   }
 
@@ -387,7 +410,7 @@ cudaError_t init_umma_attributes() {
 
 cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                              void* wt, float* partial, float* logits, int32_t* status,
-                             cudaStream_t s) {
+                             void* zero, size_t zero_bytes, cudaStream_t s) {
   (void)logits;
   const uint16_t* w_eh = static_cast<const uint16_t*>(b.gate_w);
   // W[H,E] with whole blocks of 64 experts is consumed in place as an MN-major
@@ -417,9 +440,14 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
   a.mh = plan.umma_mh;
   a.stages = pick_stages(p.E, a.mh);
   a.w_mn_major = mn_major ? 1 : 0;
+  a.zero = static_cast<uint4*>(zero);
+  a.zero_vecs = (uint32_t)(zero_bytes / 16);
   int cols = 32;
   while (cols < p.E * a.mh) cols <<= 1;
   a.tmem_cols = cols;
+  // the epilogue parks 128 rows of E*4 + 16 bytes in the operand ring
+  if ((size_t)kBlockM * (p.E * 4 + 16) > (size_t)a.stages * (a.mh * kBlockM * kBlockK * 2 + p.E * kBlockK * 2))
+    return cudaErrorInvalidValue;
   const int tile = kBlockM * a.mh;
   const dim3 grid((unsigned)((p.T + tile - 1) / tile), (unsigned)plan.ksplit);
   gate_umma_kernel<<<grid, kThreads, umma_smem_bytes(p.E, a.stages, a.mh), s>>>(map_x, map_w, a);

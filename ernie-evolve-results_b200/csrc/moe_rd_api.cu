@@ -230,15 +230,19 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   int32_t* tile_base = reinterpret_cast<int32_t*>(ws + w.tile_base);
   int32_t* ids = need_ids ? reinterpret_cast<int32_t*>(ws + w.ids) : b->expert_ids;
 
-  // status block, ticket counter and the tile counts are adjacent: one clear.
-  MOE_RD_CUDA(cudaMemsetAsync(ws + w.status, 0, w.zero_bytes, s));
+  // status block, ticket counter and the tile counts are adjacent: one clear.  The
+  // tensor-core gate clears them itself (its epilogue warps are idle while the
+  // first tiles load), which saves the separate memset node.
+  const bool gate_clears = plan.gate == MOE_RD_GATE_UMMA && p->T > 0;
+  if (!gate_clears) MOE_RD_CUDA(cudaMemsetAsync(ws + w.status, 0, w.zero_bytes, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[0], s));
   if (p->T > 0) {
     if (plan.gate == MOE_RD_GATE_SIMT) {
       MOE_RD_CUDA(launch_gate_simt(*p, *b, logits, s));
     } else if (plan.gate == MOE_RD_GATE_UMMA) {
       MOE_RD_CUDA(launch_gate_umma(*p, *b, plan, ws + w.wt,
-                                   reinterpret_cast<float*>(ws + w.partial), logits, status, s));
+                                   reinterpret_cast<float*>(ws + w.partial), logits, status,
+                                   ws + w.status, w.zero_bytes, s));
     }
   }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[1], s));
