@@ -43,6 +43,7 @@ struct Plan {
   int scatter;     // resolved MOE_RD_SCATTER_*
   int ksplit;      // split-K factor of the tensor-core gate
   int umma_mh;     // 128-token halves per CTA of the tensor-core gate (1 or 2)
+  int umma_pair;   // 1: two-CTA tiles (cta_group::2), each CTA fetching half of every W tile
 };
 
 int make_plan(const moe_rd_params& p, Plan* plan);

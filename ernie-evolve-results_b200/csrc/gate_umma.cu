@@ -124,6 +124,53 @@ __device__ __forceinline__ void bulk_store_row(void* dst, uint32_t src_smem, uin
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
+// ---- helpers of the two-CTA (cta_group::2) kernel -------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Address of the same shared-memory location in CTA `rank` of the cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// TMA load of one CTA of a pair; the bytes are counted on `bar`, a barrier of
+// the pair's leader CTA (cluster address).  No multicast: each CTA fetches
+// only what lands in its own shared memory.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+// One MMA over both CTAs of the pair: D[256, N] += A[256, 16] * B[16, N]; each
+// CTA supplies its 128 rows of A and its N/2 columns of B from the same
+// shared-memory offsets and keeps its 128 rows of D in its own TMEM.
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db,
+                                              uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Arrives on the barrier at this offset in both CTAs of the pair once all MMAs
+// issued so far have completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+      ::"r"(bar), "h"((uint16_t)3)
+      : "memory");
+}
+
 struct UmmaArgs {
   float* partial;  // [ksplit][T][E]
   int32_t* status;
@@ -134,6 +181,79 @@ struct UmmaArgs {
   uint4* zero;     // region the epilogue warps clear while the first tiles load (or null)
   uint32_t zero_vecs;
 };
+
+// Epilogue of one CTA (warps 2..5; TMEM lane = token row of the tile): waits for
+// the accumulator, parks every row in the free operand ring and writes it out
+// with one bulk copy.  `mt` numbers 128*mh-row tiles.
+__device__ __forceinline__ void epilogue_rows(const UmmaArgs& a, unsigned char* smem, uint32_t tmem_base,
+                                              uint64_t* accum_bar, volatile int* abort_flag, int warp,
+                                              int lane, int mt, int ks) {
+    const int q = warp & 3;
+    if (a.zero != nullptr) {
+      // Clear the counters of the later kernels while the first tiles are on
+      // their way (the routing kernel starts after this grid has finished).
+      const uint32_t nthr = gridDim.x * gridDim.y * 128u;
+      const uint32_t me = (blockIdx.y * gridDim.x + blockIdx.x) * 128u + (uint32_t)(q * 32 + lane);
+      for (uint32_t i = me; i < a.zero_vecs; i += nthr) a.zero[i] = make_uint4(0u, 0u, 0u, 0u);
+    }
+    bool ok = mbar_wait(smem_u32(accum_bar), 0u, abort_flag);
+    ok = __all_sync(kFull, ok);
+    if (!ok) {
+      if (lane == 0 && !*abort_flag) report(a.status, 103, mt, ks);
+      *abort_flag = 1;
+    } else {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // All MMAs have completed, so the operand ring is free: every thread parks
+      // its token row there (row pitch E*4 + 16 bytes keeps the 16-byte stores of
+      // a warp on different banks) and sends it to memory with one bulk copy.
+      const uint32_t pitch = (uint32_t)a.E * 4u + 16u;
+      unsigned char* my_row = smem + (size_t)(q * 32 + lane) * pitch;
+      for (int h = 0; h < a.mh; ++h) {
+        const int64_t row = ((int64_t)mt * a.mh + h) * kBlockM + q * 32 + lane;
+        if (h > 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        for (int c = 0; c < a.E; c += 32) {
+          uint32_t r[32];
+          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * a.E + c);
+          if (a.E - c >= 32) {
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                  "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+                  "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                  "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                  "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+                  "=r"(r[31])
+                : "r"(taddr)
+                : "memory");
+          } else {
+            // E % 32 == 16: the last 16 columns
+#pragma unroll
+            for (int i = 16; i < 32; ++i) r[i] = 0u;
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                  "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+                  "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                : "r"(taddr)
+                : "memory");
+          }
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          const int n = a.E - c >= 32 ? 32 : 16;
+          uint4* o4 = reinterpret_cast<uint4*>(my_row + (size_t)c * 4);
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (4 * i < n) o4[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        if (row < a.T)
+          bulk_store_row(a.partial + ((size_t)ks * a.T + row) * a.E, smem_u32(my_row), (uint32_t)a.E * 4u);
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -255,72 +375,7 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       if (ok) umma_commit(smem_u32(accum_bar));
     }
   } else {
-    // epilogue: TMEM lane = token row of the tile
-    const int q = warp & 3;
-    if (a.zero != nullptr) {
-      // Clear the counters of the later kernels while the first tiles are on
-      // their way (the routing kernel starts after this grid has finished).
-      const uint32_t nthr = gridDim.x * gridDim.y * 128u;
-      const uint32_t me = (blockIdx.y * gridDim.x + blockIdx.x) * 128u + (uint32_t)(q * 32 + lane);
-      for (uint32_t i = me; i < a.zero_vecs; i += nthr) a.zero[i] = make_uint4(0u, 0u, 0u, 0u);
-    }
-    bool ok = mbar_wait(smem_u32(accum_bar), 0u, abort_flag);
-    ok = __all_sync(kFull, ok);
-    if (!ok) {
-      if (lane == 0 && !*abort_flag) report(a.status, 103, mt, ks);
-      *abort_flag = 1;
-    } else {
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // All MMAs have completed, so the operand ring is free: every thread parks
-      // its token row there (row pitch E*4 + 16 bytes keeps the 16-byte stores of
-      // a warp on different banks) and sends it to memory with one bulk copy.
-      const uint32_t pitch = (uint32_t)a.E * 4u + 16u;
-      unsigned char* my_row = smem + (size_t)(q * 32 + lane) * pitch;
-      for (int h = 0; h < a.mh; ++h) {
-        const int64_t row = ((int64_t)mt * a.mh + h) * kBlockM + q * 32 + lane;
-        if (h > 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-        for (int c = 0; c < a.E; c += 32) {
-          uint32_t r[32];
-          const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(h * a.E + c);
-          if (a.E - c >= 32) {
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                  "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-                  "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-                  "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-                  "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-                  "=r"(r[31])
-                : "r"(taddr)
-                : "memory");
-          } else {
-            // E % 32 == 16: the last 16 columns
-#pragma unroll
-            for (int i = 16; i < 32; ++i) r[i] = 0u;
-            asm volatile(
-                "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-                  "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-                  "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                : "r"(taddr)
-                : "memory");
-          }
-          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-          const int n = a.E - c >= 32 ? 32 : 16;
-          uint4* o4 = reinterpret_cast<uint4*>(my_row + (size_t)c * 4);
-#pragma unroll
-          for (int i = 0; i < 8; ++i)
-            if (4 * i < n) o4[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-        }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (row < a.T)
-          bulk_store_row(a.partial + ((size_t)ks * a.T + row) * a.E, smem_u32(my_row), (uint32_t)a.E * 4u);
-      }
-      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
-    }
+    epilogue_rows(a, smem, tmem_base, accum_bar, abort_flag, warp, lane, mt, ks);
   }
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -329,6 +384,148 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     __syncwarp();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)a.tmem_cols)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Two-CTA variant for many experts (E = 256): the CTAs of a cluster of two own
+// neighbouring 128-token tiles and share every W tile - each fetches only half
+// of its columns (E/2 experts) - and the leader CTA issues one 256-row MMA over
+// both (tcgen05 cta_group::2).  A stage is then 16 KB of x + E*64 bytes of W per
+// CTA instead of 16 KB + E*128, so the same shared memory holds half as many
+// more stages and every SM pulls a third fewer bytes through L2 per tile.
+//
+// Barriers: full[s] of the LEADER counts the bytes of both CTAs (the peer's
+// TMA loads name the leader's barrier); empty[s] and accum exist in both CTAs
+// and are signalled together by a multicast commit of the leader's MMA thread.
+// ---------------------------------------------------------------------------
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gate_umma_pair_kernel(const __grid_constant__ CUtensorMap map_x,
+                      const __grid_constant__ CUtensorMap map_w, const UmmaArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t a_bytes = kBlockM * kBlockK * 2;
+  const uint32_t bh_bytes = (uint32_t)(a.E / 2) * kBlockK * 2;  // this CTA's half of a W tile
+  const uint32_t stage_bytes = a_bytes + bh_bytes;
+  unsigned char* tail = smem + (size_t)a.stages * stage_bytes;
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(tail);
+  uint64_t* empty_bar = full_bar + a.stages;
+  uint64_t* accum_bar = empty_bar + a.stages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum_bar + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const int mt = blockIdx.x, ks = blockIdx.y;
+  const int kb0 = (int)((int64_t)ks * a.kblocks / a.ksplit);
+  const int kb1 = (int)((int64_t)(ks + 1) * a.kblocks / a.ksplit);
+  const int nkb = kb1 - kb0;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(smem_u32(full_bar + s), 1);
+      mbar_init(smem_u32(empty_bar + s), 1);
+    }
+    mbar_init(smem_u32(accum_bar), 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 0) {
+    __syncwarp();
+    // the same warp of both CTAs allocates, with the same slot address
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)a.tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  cluster_sync_all();  // both CTAs' barriers are initialised before either is signalled
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      int issued = 0;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % a.stages;
+        const uint32_t use = (uint32_t)(i / a.stages);
+        if (!mbar_wait(smem_u32(empty_bar + s), (use & 1u) ^ 1u, abort_flag)) {
+          if (!*abort_flag) report(a.status, 111, mt, i);
+          *abort_flag = 1;
+          break;
+        }
+        // the leader expects the bytes of both CTAs
+        if (rank == 0) mbar_expect_tx(smem_u32(full_bar + s), 2u * stage_bytes);
+        const uint32_t fb = map_to_cta(smem_u32(full_bar + s), 0u);
+        unsigned char* st = smem + (size_t)s * stage_bytes;
+        tma_load_2d_pair(smem_u32(st), &map_x, (kb0 + i) * kBlockK, mt * kBlockM, fb);
+        if (a.w_mn_major) {
+          // this CTA's E/128 boxes of [64 h][64 e], 8 KB apart
+          const int nbox = a.E / 128;
+          for (int nb = 0; nb < nbox; ++nb)
+            tma_load_2d_pair(smem_u32(st + a_bytes + nb * 8192), &map_w, ((int)rank * nbox + nb) * 64,
+                             (kb0 + i) * kBlockK, fb);
+        } else {
+          tma_load_2d_pair(smem_u32(st + a_bytes), &map_w, (kb0 + i) * kBlockK, (int)rank * (a.E / 2), fb);
+        }
+        issued = i + 1;
+      }
+      if (*abort_flag && rank == 0) {
+        // the leader's barriers see the loads of both CTAs: wait (bounded) for the
+        // last `stages` of them before leaving
+        volatile int never = 0;
+        for (int j = issued > a.stages ? issued - a.stages : 0; j < issued; ++j)
+          mbar_wait(smem_u32(full_bar + j % a.stages), (uint32_t)(j / a.stages) & 1u, &never);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      // fp32 accumulate, bf16 x bf16, M = 256 over the pair, N = E
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.E >> 3) << 17) |
+                             ((uint32_t)((2 * kBlockM) >> 4) << 24) | (a.w_mn_major ? (1u << 16) : 0u);
+      bool ok = true;
+      for (int i = 0; i < nkb && ok; ++i) {
+        const int s = i % a.stages;
+        const uint32_t use = (uint32_t)(i / a.stages);
+        if (!mbar_wait(smem_u32(full_bar + s), use & 1u, abort_flag)) {
+          if (!*abort_flag) report(a.status, 112, mt, i);
+          *abort_flag = 1;
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        unsigned char* st = smem + (size_t)s * stage_bytes;
+        const uint64_t da = make_desc(smem_u32(st));
+        const uint64_t db = a.w_mn_major ? make_desc_mn(smem_u32(st + a_bytes), 8192u)
+                                         : make_desc(smem_u32(st + a_bytes));
+#pragma unroll
+        for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+          const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);
+          const uint64_t step_b = a.w_mn_major ? (uint64_t)((k * 2048) >> 4) : step;
+          umma_f16_pair(tmem_base, da + step, db + step_b, idesc, (i > 0 || k > 0) ? 1u : 0u);
+        }
+        umma_commit_pair(smem_u32(empty_bar + s));  // frees the stage in both CTAs
+      }
+      if (ok) umma_commit_pair(smem_u32(accum_bar));
+    }
+  } else {
+    epilogue_rows(a, smem, tmem_base, accum_bar, abort_flag, warp, lane, mt, ks);
+  }
+
+  // Neither CTA may leave (or free TMEM) while its peer can still read its shared
+  // memory, write its barriers or run an MMA into its TMEM.
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  cluster_sync_all();
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"((uint32_t)a.tmem_cols)
                  : "memory");
   }
@@ -404,7 +601,10 @@ size_t umma_smem_bytes(int E, int stages, int mh) {
 bool umma_available() { return true; }
 
 cudaError_t init_umma_attributes() {
-  return cudaFuncSetAttribute(gate_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(gate_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       227 * 1024);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gate_umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               227 * 1024);
 }
 
@@ -415,7 +615,7 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
   const uint16_t* w_eh = static_cast<const uint16_t*>(b.gate_w);
   // W[H,E] with whole blocks of 64 experts is consumed in place as an MN-major
   // operand; otherwise it is transposed to the K-major W^T[E,H] first.
-  const bool mn_major = p.w_layout == MOE_RD_W_LAYOUT_HE && p.E % 64 == 0;
+  const bool mn_major = p.w_layout == MOE_RD_W_LAYOUT_HE && p.E % (plan.umma_pair ? 128 : 64) == 0;
   if (p.w_layout == MOE_RD_W_LAYOUT_HE && !mn_major) {
     const dim3 grid((unsigned)((p.H + 31) / 32), (unsigned)((p.E + 31) / 32));
     transpose_w_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(b.gate_w),
@@ -427,8 +627,11 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
   }
   CUtensorMap map_x, map_w;
   if (!make_map(&map_x, b.x, (uint64_t)p.T, (uint64_t)p.H, kBlockM)) return cudaErrorInvalidValue;
+  const bool pair = plan.umma_pair != 0;
+  // K-major W^T: one box holds the rows (experts) one CTA needs per block of H
+  const uint32_t wt_box_rows = (uint32_t)(pair ? p.E / 2 : p.E);
   if (mn_major ? !make_map(&map_w, b.gate_w, (uint64_t)p.H, (uint64_t)p.E, 64u)
-               : !make_map(&map_w, w_eh, (uint64_t)p.E, (uint64_t)p.H, (uint32_t)p.E))
+               : !make_map(&map_w, w_eh, (uint64_t)p.E, (uint64_t)p.H, wt_box_rows))
     return cudaErrorInvalidValue;
   UmmaArgs a;
   a.partial = partial;
@@ -437,20 +640,31 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
   a.E = p.E;
   a.kblocks = p.H / kBlockK;
   a.ksplit = plan.ksplit;
-  a.mh = plan.umma_mh;
-  a.stages = pick_stages(p.E, a.mh);
+  a.mh = pair ? 1 : plan.umma_mh;
   a.w_mn_major = mn_major ? 1 : 0;
   a.zero = static_cast<uint4*>(zero);
   a.zero_vecs = (uint32_t)(zero_bytes / 16);
   int cols = 32;
   while (cols < p.E * a.mh) cols <<= 1;
   a.tmem_cols = cols;
-  // the epilogue parks 128 rows of E*4 + 16 bytes in the operand ring
-  if ((size_t)kBlockM * (p.E * 4 + 16) > (size_t)a.stages * (a.mh * kBlockM * kBlockK * 2 + p.E * kBlockK * 2))
-    return cudaErrorInvalidValue;
-  const int tile = kBlockM * a.mh;
-  const dim3 grid((unsigned)((p.T + tile - 1) / tile), (unsigned)plan.ksplit);
-  gate_umma_kernel<<<grid, kThreads, umma_smem_bytes(p.E, a.stages, a.mh), s>>>(map_x, map_w, a);
+  const size_t staging = (size_t)kBlockM * (p.E * 4 + 16);  // the epilogue parks 128 rows in the ring
+  if (pair) {
+    const int stage = kBlockM * kBlockK * 2 + (p.E / 2) * kBlockK * 2;
+    int st = MOE_RD_UMMA_SMEM_KB_ONE_CTA * 1024 / stage;
+    a.stages = st > 8 ? 8 : (st < 2 ? 2 : st);
+    if (staging > (size_t)a.stages * stage) return cudaErrorInvalidValue;
+    const unsigned mtiles = (unsigned)((p.T + kBlockM - 1) / kBlockM);
+    const dim3 grid((mtiles + 1u) & ~1u, (unsigned)plan.ksplit);  // whole pairs; rows past T load as zeros
+    const size_t smem = (size_t)a.stages * stage + (2 * a.stages + 1) * 8 + 16 + 1024;
+    gate_umma_pair_kernel<<<grid, kThreads, smem, s>>>(map_x, map_w, a);
+  } else {
+    a.stages = pick_stages(p.E, a.mh);
+    if (staging > (size_t)a.stages * (a.mh * kBlockM * kBlockK * 2 + p.E * kBlockK * 2))
+      return cudaErrorInvalidValue;
+    const int tile = kBlockM * a.mh;
+    const dim3 grid((unsigned)((p.T + tile - 1) / tile), (unsigned)plan.ksplit);
+    gate_umma_kernel<<<grid, kThreads, umma_smem_bytes(p.E, a.stages, a.mh), s>>>(map_x, map_w, a);
+  }
   count_launch();
   return cudaGetLastError();
 }

@@ -38,6 +38,8 @@ int make_plan(const moe_rd_params& p, Plan* plan) {
     else
       gate = (p.E >= 64 && umma_eligible(p)) ? MOE_RD_GATE_UMMA : MOE_RD_GATE_SIMT;
   }
+  const bool one_cta = gate == MOE_RD_GATE_UMMA_ONE_CTA;
+  if (one_cta) gate = MOE_RD_GATE_UMMA;
   if (gate == MOE_RD_GATE_UMMA && !umma_eligible(p)) return MOE_RD_E_UNSUPPORTED;
   if (gate == MOE_RD_GATE_GEMV && !gemv_eligible(p)) return MOE_RD_E_UNSUPPORTED;
   plan->gate = gate;
@@ -55,6 +57,9 @@ int make_plan(const moe_rd_params& p, Plan* plan) {
     while (ksplit < 8 && mtiles * ksplit * 2 <= 148 && kblocks / (ksplit * 2) >= 4) ksplit *= 2;
   }
   plan->umma_mh = mh;
+  // many experts: the W tiles dominate the bytes a CTA pulls in, and a pair of
+  // CTAs can share them
+  plan->umma_pair = (gate == MOE_RD_GATE_UMMA && !one_cta && p.E > 128 && p.E % 32 == 0) ? 1 : 0;
   plan->ksplit = ksplit;
   return MOE_RD_OK;
 }
@@ -96,7 +101,7 @@ static int validate(const moe_rd_params* p) {
   if (p->w_layout != MOE_RD_W_LAYOUT_HE && p->w_layout != MOE_RD_W_LAYOUT_EH) return MOE_RD_E_ENUM;
   if (p->rows_format != MOE_RD_ROWS_BF16 && p->rows_format != MOE_RD_ROWS_FP8_E4M3_B128)
     return MOE_RD_E_ENUM;
-  if (p->gate_impl < MOE_RD_GATE_AUTO || p->gate_impl > MOE_RD_GATE_GEMV) return MOE_RD_E_ENUM;
+  if (p->gate_impl < MOE_RD_GATE_AUTO || p->gate_impl > MOE_RD_GATE_UMMA_ONE_CTA) return MOE_RD_E_ENUM;
   if (p->scatter_impl < MOE_RD_SCATTER_AUTO || p->scatter_impl > MOE_RD_SCATTER_NONE)
     return MOE_RD_E_ENUM;
   if (p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128 && p->H % 128 != 0) return MOE_RD_E_SHAPE;

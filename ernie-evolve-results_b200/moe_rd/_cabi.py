@@ -14,7 +14,7 @@ SCORE_FN = {"softmax": 0, "sigmoid": 1}
 W_DTYPE = {"fp32": 0, "bf16": 1}
 W_LAYOUT = {"HE": 0, "EH": 1}
 ROWS_FORMAT = {"bf16": 0, "fp8": 1}
-GATE_IMPL = {"auto": 0, "simt": 1, "umma": 2, "external": 3, "gemv": 4}
+GATE_IMPL = {"auto": 0, "simt": 1, "umma": 2, "external": 3, "gemv": 4, "umma_one_cta": 5}
 SCATTER_IMPL = {"auto": 0, "simt": 1, "bulk": 2, "none": 3}
 
 EXPORTS = (

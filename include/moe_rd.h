@@ -46,8 +46,9 @@ enum {
   MOE_RD_GATE_SIMT = 1,     /* fixed-order fp32 FMA product, any E (defines the logit bits) */
   MOE_RD_GATE_UMMA = 2,     /* tcgen05/TMEM tiles fed by TMA (bf16 weights, E % 16 == 0, E <= 256) */
   MOE_RD_GATE_EXTERNAL = 3, /* logits supplied by the caller in router_logits */
-  MOE_RD_GATE_GEMV = 4      /* warp GEMV fused with scoring/top-k (E <= 32, weight fits in
+  MOE_RD_GATE_GEMV = 4,     /* warp GEMV fused with scoring/top-k (E <= 32, weight fits in
                                shared memory); same logit bits as MOE_RD_GATE_SIMT */
+  MOE_RD_GATE_UMMA_ONE_CTA = 5 /* MOE_RD_GATE_UMMA without the two-CTA tiles it uses for E > 128 */
 };
 enum {
   MOE_RD_SCATTER_AUTO = 0,

@@ -45,7 +45,8 @@ def test_umma_workload_shapes(name, T):
 
 
 @pytest.mark.parametrize("E,H,T,layout", [(16, 64, 50, "HE"), (64, 512, 1000, "HE"), (80, 256, 257, "EH"),
-                                          (128, 2048, 128, "EH"), (256, 1024, 2000, "HE"), (240, 192, 384, "HE")])
+                                          (128, 2048, 128, "EH"), (256, 1024, 2000, "HE"), (240, 192, 384, "HE"),
+                                          (224, 256, 300, "HE"), (256, 512, 130, "EH"), (192, 4096, 700, "HE")])
 def test_umma_shapes_layouts_and_splits(E, H, T, layout):
     g = torch.Generator().manual_seed(E + H)
     w = (torch.randn(H, E, generator=g) * 0.05).to(torch.bfloat16)
@@ -63,6 +64,19 @@ def test_umma_agrees_with_simt_gate_within_tolerance():
     a = _util.to_np(_util.run_gpu(t, kw, gate_impl="umma", return_logits=True))
     b = _util.to_np(_util.run_gpu(t, kw, gate_impl="simt", return_logits=True))
     assert np.max(np.abs(a["router_logits"] - b["router_logits"])) < LOGIT_ATOL
+
+
+@pytest.mark.parametrize("T", [1024, 77])
+def test_two_cta_tiles_give_the_logits_of_one_cta_tiles(T):
+    """E > 128 runs as pairs of CTAs that share every weight tile (cta_group::2);
+    the products and their order over H are the same, so the logits are compared
+    bit for bit with the one-CTA kernel."""
+    t, kw = workloads.make("c4", T=T)
+    a = _util.to_np(_util.run_gpu(t, kw, gate_impl="umma", return_logits=True))
+    b = _util.to_np(_util.run_gpu(t, kw, gate_impl="umma_one_cta", return_logits=True))
+    np.testing.assert_array_equal(a["router_logits"].view(np.uint32), b["router_logits"].view(np.uint32))
+    np.testing.assert_array_equal(a["expert_ids"], b["expert_ids"])
+    np.testing.assert_array_equal(a["inverse_perm"], b["inverse_perm"])
 
 
 def test_umma_full_size_c4_and_run_twice():
