@@ -85,9 +85,18 @@ void count_launch(int n = 1);
 // before it touches global memory.  This hides the launch latency between the
 // five short kernels of a call.  Without the launch attribute both
 // instructions do nothing.
-__device__ __forceinline__ void pdl_sync() {
+__device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_sync() {
+  pdl_trigger();
+  pdl_wait();
+}
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 
 // <<<grid, block, smem, stream>>> with the programmatic-serialization attribute.

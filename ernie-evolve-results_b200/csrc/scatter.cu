@@ -38,6 +38,9 @@ namespace {
 #ifndef MOE_RD_SC_BLOCKS_PER_SM
 #define MOE_RD_SC_BLOCKS_PER_SM 64  // far more blocks than fit: late blocks fill the gaps
 #endif
+#ifndef MOE_RD_SC_PREFETCH_UNITS   // work units per warp whose x is requested before the grid dependency wait
+#define MOE_RD_SC_PREFETCH_UNITS 2
+#endif
 #ifndef MOE_RD_SC_STREAMING   // 1: st.global.cs (evict-first) for the row stores
 #define MOE_RD_SC_STREAMING 1
 #endif
@@ -214,10 +217,26 @@ struct UnitWalk {
 
 template <int FMT, bool EP>
 __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterArgs a) {
-  pdl_sync();
+  pdl_trigger();
   const int lane = threadIdx.x & 31;
   const int64_t w0 = (int64_t)blockIdx.x * kScatterWarps + (threadIdx.x >> 5);
   const int64_t W = (int64_t)gridDim.x * kScatterWarps;
+  // The blocks of this grid become resident while the positions kernel is still
+  // running.  x does not depend on it, so every warp asks L2 for the slices of x
+  // it will read first and only then waits for the destinations.
+  {
+    const int n16 = a.H >> 4;
+    const int upr = FMT == MOE_RD_ROWS_BF16 ? ((a.H >> 3) + 32 * kUV - 1) / (32 * kUV) : (n16 + 31) >> 5;
+    const int unit_bytes = FMT == MOE_RD_ROWS_BF16 ? 512 * kUV : 1024;
+    const int row_bytes = a.H * 2;
+    UnitWalk pw(w0, W, upr);
+    for (int n = 0; n < MOE_RD_SC_PREFETCH_UNITS && pw.t < a.T; ++n, pw.next()) {
+      const int off = pw.c * unit_bytes + lane * 128;
+      if (lane * 128 < unit_bytes && off < row_bytes)
+        prefetch_l2(reinterpret_cast<const unsigned char*>(a.x) + (size_t)(a.T - 1 - pw.t) * row_bytes + off);
+    }
+  }
+  pdl_wait();
 
   if (FMT == MOE_RD_ROWS_BF16) {
     // unit = 32*kUV uint4 (2 KB for kUV = 4) of a row: kUV 16-byte loads per lane
