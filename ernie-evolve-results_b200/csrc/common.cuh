@@ -29,6 +29,7 @@ struct Workspace {
   size_t tile_base;    // int32[E*ntiles] per-tile counts, scanned } start of a call
                        //           in place to bases
   size_t counts;       // int32[E]  pairs per expert before dropping }
+  size_t dense;        // int32[1+kMaxK] number and first rows of identity experts }
   size_t zero_bytes;   // length of that cleared prefix
   size_t logits;       // float[T*E] when the caller passes no router_logits
   size_t ids;          // int32[T*K] when the caller passes no expert_ids
@@ -68,8 +69,9 @@ cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, c
 cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                         int32_t* tile_base, int32_t* counts, int32_t* ticket, cudaStream_t s);
 cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                           const int32_t* ids, const int32_t* tile_base, int32_t* status,
-                           cudaStream_t s, cudaEvent_t after_positions = nullptr);
+                           const int32_t* ids, const int32_t* tile_base, const int32_t* counts,
+                           int32_t* status, int32_t* dense, cudaStream_t s,
+                           cudaEvent_t after_positions = nullptr);
 bool umma_available();
 bool gemv_eligible(const moe_rd_params& p);
 void count_launch(int n = 1);

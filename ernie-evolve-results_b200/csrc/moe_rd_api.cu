@@ -71,6 +71,7 @@ void carve(const moe_rd_params& p, const Plan& plan, bool need_logits, bool need
   w->ticket = o; o += 256;
   w->tile_base = o; o += up256((size_t)p.E * plan.ntiles * 4);
   w->counts = o; o += up256((size_t)p.E * 4);
+  w->dense = o; o += 256;
   w->zero_bytes = o;
   w->logits = o; if (need_logits) o += up256((size_t)p.T * p.E * 4);
   w->ids = o; if (need_ids) o += up256((size_t)p.T * p.K * 4);
@@ -105,6 +106,9 @@ static int validate(const moe_rd_params* p) {
   if (p->scatter_impl < MOE_RD_SCATTER_AUTO || p->scatter_impl > MOE_RD_SCATTER_NONE)
     return MOE_RD_E_ENUM;
   if (p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128 && p->H % 128 != 0) return MOE_RD_E_SHAPE;
+  if (p->flags & ~MOE_RD_FLAG_SKIP_IDENTITY_ROWS) return MOE_RD_E_ENUM;
+  if ((p->flags & MOE_RD_FLAG_SKIP_IDENTITY_ROWS) && p->rows_format != MOE_RD_ROWS_BF16)
+    return MOE_RD_E_UNSUPPORTED;
   if (p->capacity < 0 || p->out_rows < 0 || p->out_rows > 0x7fffffff) return MOE_RD_E_SHAPE;
   if ((int64_t)p->E * ((p->T + kTile - 1) / kTile) > 0x7fffffff) return MOE_RD_E_TOO_LARGE;
   return MOE_RD_OK;
@@ -264,7 +268,8 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[2], s));
   MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, ticket, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[3], s));
-  MOE_RD_CUDA(launch_scatter(*p, *b, plan, ids, tile_base, status, s, ev ? ev[4] : nullptr));
+  MOE_RD_CUDA(launch_scatter(*p, *b, plan, ids, tile_base, counts, status,
+                             reinterpret_cast<int32_t*>(ws + w.dense), s, ev ? ev[4] : nullptr));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[5], s));
   return MOE_RD_OK;
 }

@@ -63,6 +63,11 @@ struct PositionArgs {
   int32_t* inverse_perm;
   uint8_t* drop_mask;
   int32_t* status;
+  const float* weights;      // [T,K] combine weights (read for row_weight)
+  int32_t* row_token;        // [out_rows] or null
+  float* row_weight;         // [out_rows] or null
+  const int32_t* counts;     // [E] pairs per expert before dropping
+  int32_t* dense;            // [1+kMaxK] identity experts: number, first rows (or null)
   int64_t T, capacity, out_rows;
   int E, K, ntiles;
 };
@@ -132,6 +137,24 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
     }
     a.inverse_perm[s] = pos;
     if (a.drop_mask != nullptr) a.drop_mask[s] = dropped ? 1 : 0;
+    if (pos >= 0) {
+      if (a.row_token != nullptr) a.row_token[pos] = (int32_t)(t0 + p / a.K);
+      if (a.row_weight != nullptr) a.row_weight[pos] = a.weights[s];
+    }
+  }
+  // Identity experts (every token once, none dropped): their first rows, in
+  // expert order, for the row scatter to skip.  At most K experts can qualify.
+  if (a.dense != nullptr && tile == 0 && warp == 0) {
+    int n = 0;
+    for (int e0 = 0; e0 < a.E; e0 += 32) {
+      const int e = e0 + lane;
+      const bool is = e < a.E && (int64_t)a.counts[e] == a.T && (a.capacity == 0 || a.T <= a.capacity);
+      const unsigned m = __ballot_sync(kFull, is);
+      const int j = n + __popc(m & ((1u << lane) - 1u));
+      if (is && j < kMaxK) a.dense[1 + j] = a.offsets[e];
+      n += __popc(m);
+    }
+    if (lane == 0) a.dense[0] = n < kMaxK ? n : kMaxK;
   }
 }
 
@@ -152,6 +175,7 @@ struct ScatterArgs {
   void* peer_rows[kMaxWorld];
   float* peer_scales[kMaxWorld];
   int epr;
+  const int32_t* dense;  // identity experts whose rows are not written (or null)
 };
 
 // Destination of pair (t,k): local row index, or (peer buffer, row) when EP.
@@ -160,6 +184,11 @@ __device__ __forceinline__ bool resolve_dest(const ScatterArgs& a, int64_t t, in
                                              void*& rows, float*& scales, int64_t& row) {
   if (q < 0) return false;
   if (!EP) {
+    if (a.dense != nullptr) {
+      const int nd = __ldg(a.dense);
+      for (int j = 0; j < nd; ++j)
+        if ((uint32_t)(q - __ldg(a.dense + 1 + j)) < (uint32_t)a.T) return false;
+    }
     rows = a.rows;
     scales = a.scales;
     row = q;
@@ -354,8 +383,9 @@ cudaError_t init_scatter_attributes() {
 }
 
 cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                           const int32_t* ids, const int32_t* tile_base, int32_t* status,
-                           cudaStream_t s, cudaEvent_t after_positions) {
+                           const int32_t* ids, const int32_t* tile_base, const int32_t* counts,
+                           int32_t* status, int32_t* dense, cudaStream_t s,
+                           cudaEvent_t after_positions) {
   if (p.T == 0) {
     return after_positions ? cudaEventRecord(after_positions, s) : cudaSuccess;
   }
@@ -366,6 +396,11 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   pa.inverse_perm = b.inverse_perm;
   pa.drop_mask = b.drop_mask;
   pa.status = status;
+  pa.weights = b.combine_weights;
+  pa.row_token = b.row_token;
+  pa.row_weight = b.row_weight;
+  pa.counts = counts;
+  pa.dense = (p.flags & MOE_RD_FLAG_SKIP_IDENTITY_ROWS) ? dense : nullptr;
   pa.T = p.T;
   pa.capacity = p.capacity;
   pa.out_rows = p.out_rows;
@@ -391,6 +426,7 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   a.T = p.T;
   a.H = p.H;
   a.K = p.K;
+  a.dense = (p.flags & MOE_RD_FLAG_SKIP_IDENTITY_ROWS) ? dense : nullptr;
   const bool fp8 = p.rows_format == MOE_RD_ROWS_FP8_E4M3_B128;
   const int64_t upr = fp8 ? ((p.H >> 4) + 31) >> 5 : ((p.H >> 3) + 32 * kUV - 1) / (32 * kUV);
   const int64_t units = p.T * upr;

@@ -21,7 +21,8 @@ import torch
 from . import _cabi
 from ._cabi import MoeRdError  # noqa: F401
 
-__all__ = ["route_dispatch", "combine", "RouteDispatchResult", "MoeRdError", "capacity_from_factor"]
+__all__ = ["route_dispatch", "combine", "gemm_plan", "expert_stats", "RouteDispatchResult", "ExpertStats",
+           "MoeRdError", "capacity_from_factor"]
 
 
 class RouteDispatchResult(NamedTuple):
@@ -34,6 +35,14 @@ class RouteDispatchResult(NamedTuple):
     expert_ids: torch.Tensor              # [T, K] int32
     router_logits: Optional[torch.Tensor]  # [T, E] fp32 when requested
     counts: torch.Tensor                  # [E] int32 pairs per expert before dropping
+    row_token: Optional[torch.Tensor] = None   # [T*K] int32 token of each permuted row, when requested
+    row_weight: Optional[torch.Tensor] = None  # [T*K] fp32 combine weight of each permuted row, when requested
+
+
+class ExpertStats(NamedTuple):
+    weight_sum: torch.Tensor   # [E] fp32, sum of the combine weights of the expert's kept rows (fixed order)
+    mean_weight: torch.Tensor  # [E] fp32, weight_sum / max(rows, 1)
+    load: torch.Tensor         # [E] fp32, rows / max(all kept rows, 1)
 
 
 def capacity_from_factor(factor: float, T: int, K: int, E: int) -> int:
@@ -50,7 +59,7 @@ _BIAS_MODES = ("none", "logit", "select", "select_and_weight")
 
 def _impl(x, gate_weight, logit_bias, select_bias, given_logits, top_k, score_fn, n_groups,
           topk_groups, group_topk, weight_from_key, renorm, routed_scale, norm_min, capacity,
-          rows_format, w_layout, gate_impl, scatter_impl, return_logits):
+          rows_format, w_layout, gate_impl, scatter_impl, return_logits, return_row_meta, flags):
     """CUDA implementation of ``moe_rd::route_dispatch`` (enqueue only, no host sync)."""
     if not x.is_cuda:
         raise RuntimeError("moe_rd.route_dispatch has no CPU path: hidden_states must be a CUDA tensor")
@@ -99,6 +108,8 @@ def _impl(x, gate_weight, logit_bias, select_bias, given_logits, top_k, score_fn
         ids = torch.empty((T, K), dtype=torch.int32, device=dev)
         drop = torch.empty((T, K), dtype=torch.uint8, device=dev)
         counts = torch.empty(E, dtype=torch.int32, device=dev)
+        row_token = torch.empty(out_rows, dtype=torch.int32, device=dev) if return_row_meta else None
+        row_weight = torch.empty(out_rows, dtype=torch.float32, device=dev) if return_row_meta else None
         if external:
             logits = given_logits
         elif return_logits:
@@ -112,28 +123,30 @@ def _impl(x, gate_weight, logit_bias, select_bias, given_logits, top_k, score_fn
             routed_scale=routed_scale, norm_min=norm_min, capacity=capacity, out_rows=out_rows,
             rows_format=rows_format, w_dtype=w_dtype, w_layout=w_layout,
             gate_impl=_cabi.GATE_IMPL["external"] if external else gate_impl,
-            scatter_impl=scatter_impl, reserved=0)
+            scatter_impl=scatter_impl, flags=int(flags))
         ws_bytes = _cabi.workspace_bytes(p)
         ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
         bufs = _cabi.Buffers(
             x=_ptr(x2), gate_w=_ptr(w), logit_bias=_ptr(logit_bias), select_bias=_ptr(select_bias),
             permuted=_ptr(permuted), scales=_ptr(scales), offsets=_ptr(offsets), inverse_perm=_ptr(inv),
             combine_weights=_ptr(weights), expert_ids=_ptr(ids), drop_mask=_ptr(drop),
-            router_logits=_ptr(logits), counts=_ptr(counts))
+            router_logits=_ptr(logits), counts=_ptr(counts), row_token=_ptr(row_token),
+            row_weight=_ptr(row_weight))
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
         _cabi.check(_cabi.lib().moe_rd_route_dispatch(
             ctypes.byref(p), ctypes.byref(bufs), ctypes.c_void_p(ws.data_ptr()), ws_bytes, stream))
         # ws goes back to the caching allocator here; reuse is ordered on this stream
     empty = torch.empty(0, device=dev)
     return [permuted, offsets, inv, weights, scales if scales is not None else empty, drop, ids,
-            logits if (logits is not None and not external) else empty, counts]
+            logits if (logits is not None and not external) else empty, counts,
+            row_token if row_token is not None else empty, row_weight if row_weight is not None else empty]
 
 
 _SCHEMA = ("route_dispatch(Tensor hidden_states, Tensor? gate_weight, Tensor? logit_bias, "
            "Tensor? select_bias, Tensor? given_logits, int top_k, int score_fn, int n_groups, "
            "int topk_groups, int group_topk, bool weight_from_key, bool renorm, float routed_scale, "
            "float norm_min, int capacity, int rows_format, int w_layout, int gate_impl, "
-           "int scatter_impl, bool return_logits) -> Tensor[]")
+           "int scatter_impl, bool return_logits, bool return_row_meta, int flags) -> Tensor[]")
 
 _torch_lib = torch.library.Library("moe_rd", "DEF")
 _torch_lib.define(_SCHEMA)
@@ -148,7 +161,8 @@ def route_dispatch(hidden_states: torch.Tensor, gate_weight: Optional[torch.Tens
                    capacity_factor: Optional[float] = None, capacity: Optional[int] = None,
                    rows_format: str = "bf16", w_layout: str = "HE", gate_impl: str = "auto",
                    scatter_impl: str = "auto", return_logits: bool = False,
-                   given_logits: Optional[torch.Tensor] = None) -> RouteDispatchResult:
+                   given_logits: Optional[torch.Tensor] = None, return_row_meta: bool = False,
+                   skip_identity_rows: bool = False) -> RouteDispatchResult:
     """Route tokens to experts and build the expert-major dispatch buffers.
 
     hidden_states: [..., H] bf16 (CUDA).  gate_weight: [H, E] (``w_layout="HE"``)
@@ -162,6 +176,12 @@ def route_dispatch(hidden_states: torch.Tensor, gate_weight: Optional[torch.Tens
     capacity / capacity_factor: rows kept per expert; later pairs (token order)
     are dropped.  rows_format "fp8" quantises rows to e4m3 with one fp32 scale
     per 128 elements.  ``given_logits`` skips the gate product.
+    ``return_row_meta`` also returns the forward permutation (token and combine
+    weight of every permuted row; the reference's ``tok`` / ``pw``,
+    kernel.cu:2172-2177).  ``skip_identity_rows`` (bf16 rows) leaves the rows of
+    an expert that received every token unwritten - they would be a copy of
+    ``hidden_states`` - for ``gemm_plan`` to aim that expert at ``hidden_states``
+    (the reference's identity shortcut, kernel.cu:2089-2108).
     """
     if bias_mode not in _BIAS_MODES:
         raise ValueError(f"bias_mode must be one of {_BIAS_MODES}")
@@ -179,14 +199,16 @@ def route_dispatch(hidden_states: torch.Tensor, gate_weight: Optional[torch.Tens
         _cabi.SCORE_FN[score_fn], n_groups, topk_groups, group_topk,
         bias_mode == "select_and_weight", renorm, float(routed_scale), float(norm_min),
         int(capacity), _cabi.ROWS_FORMAT[rows_format], _cabi.W_LAYOUT[w_layout],
-        _cabi.GATE_IMPL[gate_impl], _cabi.SCATTER_IMPL[scatter_impl], return_logits)
-    permuted, offsets, inv, weights, scales, drop, ids, logits, counts = out
+        _cabi.GATE_IMPL[gate_impl], _cabi.SCATTER_IMPL[scatter_impl], return_logits, return_row_meta,
+        _cabi.FLAG_SKIP_IDENTITY_ROWS if skip_identity_rows else 0)
+    permuted, offsets, inv, weights, scales, drop, ids, logits, counts, row_token, row_weight = out
     if given_logits is not None:
         logits = given_logits
     elif not return_logits:
         logits = None
     return RouteDispatchResult(permuted, offsets, inv, weights,
-                               scales if rows_format == "fp8" else None, drop, ids, logits, counts)
+                               scales if rows_format == "fp8" else None, drop, ids, logits, counts,
+                               row_token if return_row_meta else None, row_weight if return_row_meta else None)
 
 
 def _combine_impl(y, inverse_perm, combine_weights, shared):
@@ -219,3 +241,55 @@ def combine(y: torch.Tensor, inverse_perm: torch.Tensor, combine_weights: torch.
     applied: ``y`` holds the expert outputs in expert-major row order.  Mirrors
     the reference's combine_kernel (kernel.cu:2365-2428)."""
     return torch.ops.moe_rd.combine(y, inverse_perm, combine_weights, shared)
+
+
+def gemm_plan(offsets: torch.Tensor, rows: torch.Tensor, expert_weights: torch.Tensor, out: torch.Tensor,
+              identity_source: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Device-side plan of the ragged expert GEMM ``out[rows of e] = rows[rows of e] @ expert_weights[e]``.
+
+    Returns a uint8 tensor [E, sizeof(moe_rd_gemm_group)] holding one
+    ``moe_rd_gemm_group`` per expert (problem shape, A / B / D pointers, pitches),
+    built on the current stream from ``offsets`` without a host synchronisation;
+    ``decode_gemm_plan`` reads it back.  With ``identity_source`` (the un-permuted
+    hidden states), an expert that holds every token reads it instead of its
+    slice of ``rows``.  Mirrors the reference's plan_kernel (moe_gemm.cu:613-638).
+    """
+    if not offsets.is_cuda or offsets.dtype != torch.int32:
+        raise TypeError("offsets must be a CUDA int32 tensor")
+    E = offsets.numel() - 1
+    if expert_weights.shape[0] != E:
+        raise ValueError("expert_weights must have one leading slice per expert")
+    k = rows.shape[-1]
+    n = out.shape[-1]
+    ident_m = 0 if identity_source is None else identity_source.numel() // identity_source.shape[-1]
+    with torch.cuda.device(offsets.device):
+        plan = torch.empty((E, ctypes.sizeof(_cabi.GemmGroup)), dtype=torch.uint8, device=offsets.device)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(offsets.device).cuda_stream)
+        _cabi.check(_cabi.lib().moe_rd_gemm_plan(
+            _ptr(offsets), E, _ptr(rows), rows.stride(0) * rows.element_size(), _ptr(identity_source), ident_m,
+            _ptr(expert_weights), expert_weights.stride(0) * expert_weights.element_size(), _ptr(out),
+            out.stride(0) * out.element_size(), n, k, _ptr(plan), stream))
+    return plan
+
+
+def decode_gemm_plan(plan: torch.Tensor):
+    """Host copy of a ``gemm_plan`` result as a list of ``_cabi.GemmGroup`` (synchronises)."""
+    raw = plan.cpu().numpy().tobytes()
+    size = ctypes.sizeof(_cabi.GemmGroup)
+    return [_cabi.GemmGroup.from_buffer_copy(raw[i * size:(i + 1) * size]) for i in range(plan.shape[0])]
+
+
+def expert_stats(offsets: torch.Tensor, row_weight: torch.Tensor) -> ExpertStats:
+    """Per-expert sum and mean of the combine weights of the kept rows, and the
+    share of rows each expert received; the sums are added in a fixed order, so
+    repeated runs give the same bits (the reference's wsum / counts,
+    kernel.cu:1903-1919, made outputs)."""
+    if not offsets.is_cuda or offsets.dtype != torch.int32 or row_weight.dtype != torch.float32:
+        raise TypeError("expert_stats expects CUDA int32 offsets and float32 row weights")
+    E = offsets.numel() - 1
+    with torch.cuda.device(offsets.device):
+        ws, mw, ld = (torch.empty(E, dtype=torch.float32, device=offsets.device) for _ in range(3))
+        stream = ctypes.c_void_p(torch.cuda.current_stream(offsets.device).cuda_stream)
+        _cabi.check(_cabi.lib().moe_rd_expert_stats(_ptr(offsets), _ptr(row_weight.contiguous()), E, _ptr(ws), _ptr(mw),
+                                                    _ptr(ld), stream))
+    return ExpertStats(ws, mw, ld)

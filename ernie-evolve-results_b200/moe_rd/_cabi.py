@@ -20,7 +20,7 @@ SCATTER_IMPL = {"auto": 0, "simt": 1, "bulk": 2, "none": 3}
 EXPORTS = (
     "moe_rd_workspace_bytes", "moe_rd_route_dispatch", "moe_rd_route_dispatch_noalloc",
     "moe_rd_route_dispatch_timed", "moe_rd_read_status", "moe_rd_ep_unpack", "moe_rd_ep_plan", "moe_rd_combine",
-    "moe_rd_ep_scatter",
+    "moe_rd_ep_scatter", "moe_rd_gemm_plan", "moe_rd_expert_stats",
     "moe_rd_launch_count", "moe_rd_strerror", "moe_rd_last_cuda_error", "moe_rd_version",
 )
 
@@ -34,14 +34,25 @@ class Params(ctypes.Structure):
         ("routed_scale", ctypes.c_float), ("norm_min", ctypes.c_float),
         ("capacity", ctypes.c_int64), ("out_rows", ctypes.c_int64),
         ("rows_format", ctypes.c_int32), ("w_dtype", ctypes.c_int32), ("w_layout", ctypes.c_int32),
-        ("gate_impl", ctypes.c_int32), ("scatter_impl", ctypes.c_int32), ("reserved", ctypes.c_int32),
+        ("gate_impl", ctypes.c_int32), ("scatter_impl", ctypes.c_int32), ("flags", ctypes.c_int32),
     ]
 
 
 class Buffers(ctypes.Structure):
     _fields_ = [(n, ctypes.c_void_p) for n in (
         "x", "gate_w", "logit_bias", "select_bias", "permuted", "scales", "offsets",
-        "inverse_perm", "combine_weights", "expert_ids", "drop_mask", "router_logits", "counts")]
+        "inverse_perm", "combine_weights", "expert_ids", "drop_mask", "router_logits", "counts",
+        "row_token", "row_weight")]
+
+
+class GemmGroup(ctypes.Structure):
+    """moe_rd_gemm_group of include/moe_rd.h."""
+    _fields_ = [("m", ctypes.c_int32), ("n", ctypes.c_int32), ("k", ctypes.c_int32), ("identity", ctypes.c_int32),
+                ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("d", ctypes.c_void_p),
+                ("lda", ctypes.c_int64), ("ldb", ctypes.c_int64), ("ldd", ctypes.c_int64)]
+
+
+FLAG_SKIP_IDENTITY_ROWS = 1
 
 
 class MoeRdError(RuntimeError):
@@ -87,6 +98,13 @@ def lib() -> ctypes.CDLL:
         L.moe_rd_combine.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p,
                                      ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         L.moe_rd_combine.restype = ctypes.c_int
+        L.moe_rd_gemm_plan.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p,
+                                       ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64,
+                                       ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p]
+        L.moe_rd_gemm_plan.restype = ctypes.c_int
+        L.moe_rd_expert_stats.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_void_p,
+                                          ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        L.moe_rd_expert_stats.restype = ctypes.c_int
         L.moe_rd_read_status.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         L.moe_rd_read_status.restype = ctypes.c_int
         L.moe_rd_launch_count.argtypes = []

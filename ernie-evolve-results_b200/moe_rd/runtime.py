@@ -48,7 +48,7 @@ class Session:
             out_rows=out_rows, rows_format=_cabi.ROWS_FORMAT[rows_format],
             w_dtype=_cabi.W_DTYPE["fp32" if w_dtype == torch.float32 else "bf16"],
             w_layout=_cabi.W_LAYOUT[w_layout], gate_impl=_cabi.GATE_IMPL[gate_impl],
-            scatter_impl=_cabi.SCATTER_IMPL[scatter_impl], reserved=0)
+            scatter_impl=_cabi.SCATTER_IMPL[scatter_impl], flags=0)
         self.ws_bytes = _cabi.workspace_bytes(self.params)
         self.workspace = torch.empty(self.ws_bytes, dtype=torch.uint8, device=d)
 
@@ -61,7 +61,8 @@ class Session:
             x=ptr(x), gate_w=ptr(w), logit_bias=ptr(lb), select_bias=ptr(sb), permuted=ptr(self.permuted),
             scales=ptr(self.scales), offsets=ptr(self.offsets), inverse_perm=ptr(self.inverse_perm),
             combine_weights=ptr(self.combine_weights), expert_ids=ptr(self.expert_ids),
-            drop_mask=ptr(self.drop_mask), router_logits=ptr(self.router_logits), counts=ptr(self.counts))
+            drop_mask=ptr(self.drop_mask), router_logits=ptr(self.router_logits), counts=ptr(self.counts),
+            row_token=None, row_weight=None)
 
     def _check_inputs(self, x, w):
         if not (x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and tuple(x.shape) == (self.T, self.H)):

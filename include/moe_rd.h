@@ -85,8 +85,19 @@ typedef struct moe_rd_params {
   int32_t w_layout;     /* MOE_RD_W_LAYOUT_* */
   int32_t gate_impl;    /* MOE_RD_GATE_* */
   int32_t scatter_impl; /* MOE_RD_SCATTER_* */
-  int32_t reserved;
+  int32_t flags;        /* MOE_RD_FLAG_* bits, 0 by default */
 } moe_rd_params;
+
+/*
+ * MOE_RD_FLAG_SKIP_IDENTITY_ROWS (bf16 rows): an expert that received every one
+ * of the T tokens (none dropped) holds them exactly once each and in token
+ * order, so its slice of `permuted` would be a verbatim copy of x.  With this
+ * flag the rows of such experts are not written (their positions in offsets /
+ * inverse_perm stay as they are); moe_rd_gemm_plan aims the A pointer of those
+ * groups at x instead.  Same shortcut as ident_a / ident_m of the reference
+ * (moe_gemm.h:66-75, kernel.cu:2089-2108, 2154).
+ */
+enum { MOE_RD_FLAG_SKIP_IDENTITY_ROWS = 1 };
 
 /*
  * Device buffers.  The data contract between routing and expert compute that
@@ -108,6 +119,9 @@ typedef struct moe_rd_buffers {
   uint8_t* drop_mask;        /* [T,K] 1 = dropped by the capacity limit, or NULL */
   float* router_logits;      /* [T,E] fp32: optional output; INPUT for MOE_RD_GATE_EXTERNAL */
   int32_t* counts;           /* [E] pairs routed to each expert before dropping, or NULL */
+  int32_t* row_token;        /* [out_rows] token of each permuted row (the reference's forward
+                                permutation `tok` / `ptok`, kernel.cu:2172-2177), or NULL */
+  float* row_weight;         /* [out_rows] combine weight of each permuted row (`pw`), or NULL */
 } moe_rd_buffers;
 
 /* Bytes of scratch moe_rd_route_dispatch needs for these parameters. */
@@ -232,6 +246,46 @@ int moe_rd_route_dispatch_timed(const moe_rd_params* p, const moe_rd_buffers* b,
  * on external compute-sanitizer runs (kernel.cu:4193-4195).
  */
 int moe_rd_read_status(const void* workspace, void* stream, int32_t status[8]);
+
+/*
+ * One group of a grouped (ragged) expert GEMM  D[m,n] = A[m,k] * B_e : what
+ * plan_kernel of the reference builds per expert on the device from the routed
+ * offsets (moe_gemm.cu:613-638: problem shape, A / B / D pointers, leading
+ * dimensions), as plain integers and pointers.
+ */
+typedef struct moe_rd_gemm_group {
+  int32_t m, n, k;      /* rows of this expert, output columns, reduction length */
+  int32_t identity;     /* 1: A is aimed at ident_a (every token once, in token order) */
+  const void* a;        /* first row of the group's A operand */
+  const void* b;        /* this expert's weight */
+  void* d;              /* first row of the group's output */
+  int64_t lda, ldb, ldd; /* row pitches in bytes of A and D, bytes per expert of B */
+} moe_rd_gemm_group;
+
+/*
+ * Builds groups[E] on the device from offsets[E+1] with no host
+ * synchronisation.  a_rows is the permuted buffer (row pitch a_row_bytes), w
+ * the stacked expert weights (w_expert_bytes apart), d_rows the output (row
+ * pitch d_row_bytes).  ident_a / ident_m: when ident_m > 0, a group with
+ * exactly ident_m rows reads ident_a (the un-permuted x) instead of its slice
+ * of a_rows (see MOE_RD_FLAG_SKIP_IDENTITY_ROWS).
+ */
+int moe_rd_gemm_plan(const int32_t* offsets, int32_t E, const void* a_rows, int64_t a_row_bytes,
+                     const void* ident_a, int64_t ident_m, const void* w, int64_t w_expert_bytes,
+                     void* d_rows, int64_t d_row_bytes, int32_t n, int32_t k,
+                     moe_rd_gemm_group* groups, void* stream);
+
+/*
+ * Per-expert statistics of one routing pass, as first-class outputs (the
+ * reference keeps wsum / counts for its own use, kernel.cu:1903-1919):
+ * weight_sum[e] = sum of row_weight over the expert's kept rows, added in a
+ * fixed order (element i goes to partial i % 256 in ascending order, the 256
+ * partials are combined by the tree v[i] += v[i + off], off = 128..1), so the
+ * result does not depend on scheduling; mean_weight[e] = weight_sum[e] /
+ * max(rows, 1); load[e] = rows / max(total kept rows, 1).  Any output may be NULL.
+ */
+int moe_rd_expert_stats(const int32_t* offsets, const float* row_weight, int32_t E,
+                        float* weight_sum, float* mean_weight, float* load, void* stream);
 
 /* Kernels this library launched since it was loaded (all threads). */
 int64_t moe_rd_launch_count(void);

@@ -210,6 +210,70 @@ def combine(y_u16, inverse_perm, weights, shared_u16=None):
     return out
 
 
+def row_meta(inverse_perm, weights, n_rows):
+    """Forward permutation: token and combine weight of every permuted row
+    (the reference's tok / pw, kernel.cu:2172-2177).  Rows nobody maps to keep
+    token -1 and weight 0."""
+    inv = np.asarray(inverse_perm, dtype=np.int64)
+    T, K = inv.shape
+    tok = np.full(n_rows, -1, dtype=np.int32)
+    wt = np.zeros(n_rows, dtype=np.float32)
+    t_idx = np.repeat(np.arange(T, dtype=np.int32), K).reshape(T, K)
+    keep = inv >= 0
+    tok[inv[keep]] = t_idx[keep]
+    wt[inv[keep]] = np.asarray(weights, dtype=np.float32)[keep]
+    return tok, wt
+
+
+def expert_stats(offsets, row_weight):
+    """Per-expert weight sum in the fixed order the statistics kernel states:
+    element i of an expert's rows is added (fp32, ascending i) to partial i % 256,
+    the partials are combined by the tree v[i] += v[i + off], off = 128..1;
+    mean = sum / max(rows, 1); load = rows / max(all rows, 1).  (The reference
+    accumulates wsum with atomics in no fixed order, kernel.cu:1903-1919.)"""
+    offsets = np.asarray(offsets, dtype=np.int64)
+    w = np.asarray(row_weight, dtype=np.float32)
+    E = offsets.size - 1
+    wsum = np.zeros(E, dtype=np.float32)
+    mean = np.zeros(E, dtype=np.float32)
+    load = np.zeros(E, dtype=np.float32)
+    total = np.float32(max(int(offsets[E]), 1))
+    for e in range(E):
+        seg = w[offsets[e]:offsets[e + 1]]
+        rows = seg.size
+        pad = (-rows) % 256
+        # padding with +0.0 leaves every partial unchanged except that -0.0 + 0.0 = +0.0,
+        # which is also what a partial that starts from +0.0 gives
+        m = np.concatenate([seg, np.zeros(pad, dtype=np.float32)]).reshape(-1, 256)
+        acc = np.zeros(256, dtype=np.float32)
+        for r in range(m.shape[0]):
+            acc = (acc + m[r]).astype(np.float32)
+        off = 128
+        while off:
+            acc[:off] = (acc[:off] + acc[off:2 * off]).astype(np.float32)
+            off >>= 1
+        wsum[e] = acc[0]
+        mean[e] = np.float32(acc[0]) / np.float32(max(rows, 1))
+        load[e] = np.float32(rows) / total
+    return wsum, mean, load
+
+
+def gemm_plan(offsets, a_base, a_row_bytes, w_base, w_expert_bytes, d_base, d_row_bytes, n, k,
+              ident_base=0, ident_m=0):
+    """Groups of the ragged expert GEMM as the reference's plan_kernel lays them
+    out (moe_gemm.cu:613-638): (m, n, k, identity, a, b, d) per expert, with
+    addresses as integers."""
+    offsets = np.asarray(offsets, dtype=np.int64)
+    out = []
+    for e in range(offsets.size - 1):
+        start, m = int(offsets[e]), int(offsets[e + 1] - offsets[e])
+        ident = bool(ident_m > 0 and m == ident_m and ident_base)
+        out.append(dict(m=m, n=n, k=k, identity=int(ident),
+                        a=ident_base if ident else a_base + start * a_row_bytes,
+                        b=w_base + e * w_expert_bytes, d=d_base + start * d_row_bytes))
+    return out
+
+
 def set_threads(n: int) -> None:
     lib().moe_oracle_set_threads(int(n))
 

@@ -33,7 +33,7 @@ def test_library_exports_every_declared_symbol():
 def params(**over):
     base = dict(T=1024, H=1024, E=8, K=2, n_groups=1, topk_groups=1, group_topk=1, score_fn=0,
                 weight_from_key=0, renorm=1, routed_scale=1.0, norm_min=1e-20, capacity=0,
-                out_rows=2048, rows_format=0, w_dtype=1, w_layout=0, gate_impl=0, scatter_impl=0, reserved=0)
+                out_rows=2048, rows_format=0, w_dtype=1, w_layout=0, gate_impl=0, scatter_impl=0, flags=0)
     base.update(over)
     return _cabi.Params(**base)
 
@@ -41,7 +41,9 @@ def params(**over):
 def test_struct_layout_matches_header():
     # int64 T, 11 x 4-byte fields, pad?, int64 capacity, int64 out_rows, 6 x int32
     assert ctypes.sizeof(_cabi.Params) == 8 + 4 * 11 + 4 + 16 + 24
-    assert ctypes.sizeof(_cabi.Buffers) == 13 * ctypes.sizeof(ctypes.c_void_p)
+    assert ctypes.sizeof(_cabi.Buffers) == 15 * ctypes.sizeof(ctypes.c_void_p)
+    # moe_rd_gemm_group: 4 x int32, 3 pointers, 3 x int64
+    assert ctypes.sizeof(_cabi.GemmGroup) == 16 + 24 + 24
 
 
 def test_workspace_bytes_and_validation():
@@ -51,7 +53,8 @@ def test_workspace_bytes_and_validation():
     bad = [dict(H=1001), dict(E=0), dict(E=257), dict(K=0), dict(K=9), dict(K=33, E=64),
            dict(n_groups=3), dict(E=64, K=8, n_groups=8, topk_groups=0, group_topk=2),
            dict(E=64, K=8, n_groups=16, topk_groups=1, group_topk=2), dict(score_fn=7),
-           dict(rows_format=1, H=1000), dict(capacity=-1), dict(T=-1), dict(gate_impl=9), dict(w_dtype=3)]
+           dict(rows_format=1, H=1000), dict(capacity=-1), dict(T=-1), dict(gate_impl=9), dict(w_dtype=3),
+           dict(flags=2), dict(flags=1, rows_format=1)]
     for o in bad:
         with pytest.raises(_cabi.MoeRdError):
             _cabi.workspace_bytes(params(**o))

@@ -320,3 +320,30 @@ def test_combine_matches_numpy_restatement():
             acc[sel] = (prod + acc[sel].astype(np.float64)).astype(np.float32)  # one fused multiply-add
         ref = torch.from_numpy(acc).to(torch.bfloat16)
         np.testing.assert_array_equal(got, _util.bf16_bits(ref))
+
+
+def test_row_meta_expert_stats_and_plan_restatements():
+    inv = np.array([[2, 0], [-1, 1], [3, 4]], dtype=np.int32)
+    w = np.array([[0.5, 0.25], [0.125, 1.0], [2.0, 4.0]], dtype=np.float32)
+    tok, wt = cpu_oracle.row_meta(inv, w, 6)
+    assert list(tok) == [0, 1, 0, 2, 2, -1]
+    assert list(wt) == [0.25, 1.0, 0.5, 2.0, 4.0, 0.0]
+    offs = np.array([0, 2, 2, 5], dtype=np.int32)
+    ws, mw, ld = cpu_oracle.expert_stats(offs, wt)
+    assert list(ws) == [1.25, 0.0, 6.5] and list(mw) == [0.625, 0.0, np.float32(6.5) / np.float32(3)]
+    assert np.allclose(ld, [0.4, 0.0, 0.6])
+    # order: 600 equal tiny weights next to a large one do not depend on numpy's pairwise sum
+    big = np.concatenate([[1e8], np.full(599, 1.0)]).astype(np.float32)
+    s, _, _ = cpu_oracle.expert_stats(np.array([0, 600]), big)
+    part = np.zeros(256, dtype=np.float32)
+    for i, v in enumerate(big):
+        part[i % 256] = np.float32(part[i % 256] + v)
+    off = 128
+    while off:
+        part[:off] = part[:off] + part[off:2 * off]
+        off >>= 1
+    assert s[0] == part[0]
+    plan = cpu_oracle.gemm_plan(offs, 1000, 16, 5000, 64, 9000, 8, n=4, k=8, ident_base=77, ident_m=3)
+    assert [g["m"] for g in plan] == [2, 0, 3]
+    assert plan[0]["a"] == 1000 and plan[2]["a"] == 77 and plan[2]["identity"] == 1
+    assert plan[2]["b"] == 5000 + 2 * 64 and plan[2]["d"] == 9000 + 2 * 8

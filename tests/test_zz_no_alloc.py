@@ -41,7 +41,7 @@ def _setup(name, T, H):
         weight_from_key=int(mode == "select_and_weight"), renorm=int(kw.get("renorm", True)),
         routed_scale=kw.get("routed_scale", 1.0), norm_min=1e-20, capacity=cap, out_rows=out_rows,
         rows_format=int(fp8), w_dtype=_cabi.W_DTYPE["fp32" if w.dtype == torch.float32 else "bf16"],
-        w_layout=0, gate_impl=0, scatter_impl=0, reserved=0)
+        w_layout=0, gate_impl=0, scatter_impl=0, flags=0)
 
     def outputs():
         o = dict(
@@ -108,7 +108,7 @@ def test_noalloc_refuses_problems_beyond_its_scratch():
     p = _cabi.Params(T=400000, H=1024, E=256, K=8, n_groups=1, topk_groups=1, group_topk=1, score_fn=0,
                      weight_from_key=0, renorm=1, routed_scale=1.0, norm_min=1e-20, capacity=0,
                      out_rows=3200000, rows_format=0, w_dtype=1, w_layout=0, gate_impl=1, scatter_impl=0,
-                     reserved=0)
+                     flags=0)
     assert _cabi.workspace_bytes(p) > NOALLOC_MAX_BYTES
     b = _cabi.Buffers()
     rc = L.moe_rd_route_dispatch_noalloc(ctypes.byref(p), ctypes.byref(b), None)
