@@ -10,6 +10,13 @@
 // (inverse_perm < 0) contribute nothing.  Work units (a token x 32 vectors of
 // 16 bytes) are dealt to warps grid-stride with many more blocks than fit, as
 // in the row scatter.
+//
+// Expert-parallel form (EP == true): the expert outputs stay where the experts
+// ran.  The row of pair (t,k) then lives on rank ids[t,k] / experts_per_rank, at
+// the row the dispatch stored it to, and is fetched from there with plain
+// 16-byte peer loads over NVLink inside the same kernel that weights and adds
+// it: the return all-to-all and the un-permute are one pass, and no receive
+// buffer exists.  Arithmetic and order are those of the local form.
 #include "common.cuh"
 
 namespace moe_rd {
@@ -27,14 +34,29 @@ struct CombineArgs {
   uint4* out;
   int64_t T;
   int nvec, K;
+  // EP: y of rank d is peer_y[d]; pair (t,k) of expert e is row
+  // dest_base[e] + (inverse_perm[t,k] - offsets[e]) there
+  const uint4* peer_y[8];
+  const int32_t* ids;
+  const int32_t* offsets;
+  const int32_t* dest_base;
+  int epr;
 };
+
+template <bool EP>
+__device__ __forceinline__ const uint4* row_of(const CombineArgs& a, int64_t t, int k, int pos) {
+  if (!EP) return a.y + (size_t)pos * a.nvec;
+  const int e = __ldg(a.ids + (size_t)t * a.K + k);
+  const int64_t row = (int64_t)__ldg(a.dest_base + e) + (pos - __ldg(a.offsets + e));
+  return a.peer_y[e / a.epr] + (size_t)row * a.nvec;
+}
 
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 
-template <int KT>
+template <int KT, bool EP>
 __device__ __forceinline__ void combine_unit(const CombineArgs& a, int64_t t, int v) {
   int pos[KT];
   float w[KT];
@@ -46,7 +68,7 @@ __device__ __forceinline__ void combine_unit(const CombineArgs& a, int64_t t, in
   }
 #pragma unroll
   for (int k = 0; k < KT; ++k)
-    if (pos[k] >= 0) yv[k] = __ldcs(a.y + (size_t)pos[k] * a.nvec + v);
+    if (pos[k] >= 0) yv[k] = __ldcs(row_of<EP>(a, t, k, pos[k]) + v);
   float acc[8];
   if (a.shared != nullptr) {
     const uint4 s = __ldcs(a.shared + (size_t)t * a.nvec + v);
@@ -73,6 +95,7 @@ __device__ __forceinline__ void combine_unit(const CombineArgs& a, int64_t t, in
 }
 
 // K > 8: same arithmetic with the loads issued eight at a time.
+template <bool EP>
 __device__ __forceinline__ void combine_unit_any(const CombineArgs& a, int64_t t, int v) {
   float acc[8];
   if (a.shared != nullptr) {
@@ -93,7 +116,7 @@ __device__ __forceinline__ void combine_unit_any(const CombineArgs& a, int64_t t
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k)
-      if (pos[k] >= 0) yv[k] = __ldcs(a.y + (size_t)pos[k] * a.nvec + v);
+      if (pos[k] >= 0) yv[k] = __ldcs(row_of<EP>(a, t, k0 + k, pos[k]) + v);
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       if (pos[k] >= 0) {
@@ -112,7 +135,7 @@ __device__ __forceinline__ void combine_unit_any(const CombineArgs& a, int64_t t
   __stcs(a.out + (size_t)t * a.nvec + v, o);
 }
 
-template <int KT>
+template <int KT, bool EP>
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineArgs a) {
   pdl_sync();
   const int lane = threadIdx.x & 31;
@@ -124,9 +147,9 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(const CombineA
     const int v = (int)(u - t * upr) * 32 + lane;
     if (v >= a.nvec) continue;
     if (KT > 0)
-      combine_unit<(KT > 0 ? KT : 1)>(a, t, v);
+      combine_unit<(KT > 0 ? KT : 1), EP>(a, t, v);
     else
-      combine_unit_any(a, t, v);
+      combine_unit_any<EP>(a, t, v);
   }
 }
 
@@ -138,22 +161,11 @@ int device_sms();
 
 using namespace moe_rd;
 
-extern "C" int moe_rd_combine(int64_t T, int32_t H, int32_t K, const void* y,
-                              const int32_t* inverse_perm, const float* combine_weights,
-                              const void* shared, void* out, void* stream) {
-  if (T < 0 || H < 8 || H % 8 != 0 || K < 1 || K > kMaxK) return MOE_RD_E_SHAPE;
-  if (T == 0) return MOE_RD_OK;
-  if (y == nullptr || inverse_perm == nullptr || combine_weights == nullptr || out == nullptr)
-    return MOE_RD_E_NULL;
-  if ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out) |
-       reinterpret_cast<uintptr_t>(shared)) & 15)
-    return MOE_RD_E_ALIGN;
-  CombineArgs a;
-  a.y = static_cast<const uint4*>(y);
-  a.inverse_perm = inverse_perm;
-  a.weights = combine_weights;
-  a.shared = static_cast<const uint4*>(shared);
-  a.out = static_cast<uint4*>(out);
+namespace moe_rd {
+namespace {
+
+template <bool EP>
+int launch_combine(CombineArgs& a, int64_t T, int32_t H, int32_t K, void* stream) {
   a.T = T;
   a.nvec = H / 8;
   a.K = K;
@@ -164,13 +176,65 @@ extern "C" int moe_rd_combine(int64_t T, int32_t H, int32_t K, const void* y,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   cudaError_t e;
   if (K <= 2)
-    e = launch_pdl(combine_kernel<2>, grid, dim3(kCombineThreads), 0, s, a);
+    e = launch_pdl(combine_kernel<2, EP>, grid, dim3(kCombineThreads), 0, s, a);
   else if (K <= 4)
-    e = launch_pdl(combine_kernel<4>, grid, dim3(kCombineThreads), 0, s, a);
+    e = launch_pdl(combine_kernel<4, EP>, grid, dim3(kCombineThreads), 0, s, a);
   else if (K <= 8)
-    e = launch_pdl(combine_kernel<8>, grid, dim3(kCombineThreads), 0, s, a);
+    e = launch_pdl(combine_kernel<8, EP>, grid, dim3(kCombineThreads), 0, s, a);
   else
-    e = launch_pdl(combine_kernel<0>, grid, dim3(kCombineThreads), 0, s, a);
+    e = launch_pdl(combine_kernel<0, EP>, grid, dim3(kCombineThreads), 0, s, a);
   count_launch();
   return e == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
+}
+
+}  // namespace
+}  // namespace moe_rd
+
+extern "C" int moe_rd_combine(int64_t T, int32_t H, int32_t K, const void* y,
+                              const int32_t* inverse_perm, const float* combine_weights,
+                              const void* shared, void* out, void* stream) {
+  if (T < 0 || H < 8 || H % 8 != 0 || K < 1 || K > kMaxK) return MOE_RD_E_SHAPE;
+  if (T == 0) return MOE_RD_OK;
+  if (y == nullptr || inverse_perm == nullptr || combine_weights == nullptr || out == nullptr)
+    return MOE_RD_E_NULL;
+  if ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out) |
+       reinterpret_cast<uintptr_t>(shared)) & 15)
+    return MOE_RD_E_ALIGN;
+  CombineArgs a = {};
+  a.y = static_cast<const uint4*>(y);
+  a.inverse_perm = inverse_perm;
+  a.weights = combine_weights;
+  a.shared = static_cast<const uint4*>(shared);
+  a.out = static_cast<uint4*>(out);
+  return launch_combine<false>(a, T, H, K, stream);
+}
+
+extern "C" int moe_rd_ep_combine(int64_t T, int32_t H, int32_t K, int32_t E, int32_t world,
+                                 const void* const* peer_y, const int32_t* expert_ids,
+                                 const int32_t* inverse_perm, const float* combine_weights,
+                                 const int32_t* offsets, const int32_t* dest_base, const void* shared,
+                                 void* out, void* stream) {
+  if (T < 0 || H < 8 || H % 8 != 0 || K < 1 || K > kMaxK || world < 1 || world > 8 || E < 1 || E > kMaxE ||
+      E % world != 0)
+    return MOE_RD_E_SHAPE;
+  if (T == 0) return MOE_RD_OK;
+  if (peer_y == nullptr || expert_ids == nullptr || inverse_perm == nullptr || combine_weights == nullptr ||
+      offsets == nullptr || dest_base == nullptr || out == nullptr)
+    return MOE_RD_E_NULL;
+  CombineArgs a = {};
+  for (int d = 0; d < world; ++d) {
+    if (peer_y[d] == nullptr) return MOE_RD_E_NULL;
+    if (reinterpret_cast<uintptr_t>(peer_y[d]) & 15) return MOE_RD_E_ALIGN;
+    a.peer_y[d] = static_cast<const uint4*>(peer_y[d]);
+  }
+  if ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(shared)) & 15) return MOE_RD_E_ALIGN;
+  a.inverse_perm = inverse_perm;
+  a.weights = combine_weights;
+  a.shared = static_cast<const uint4*>(shared);
+  a.out = static_cast<uint4*>(out);
+  a.ids = expert_ids;
+  a.offsets = offsets;
+  a.dest_base = dest_base;
+  a.epr = E / world;
+  return launch_combine<true>(a, T, H, K, stream);
 }

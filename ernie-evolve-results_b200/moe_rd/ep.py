@@ -192,3 +192,39 @@ class ExpertParallelFused:
                                         self.peer_rows, self.peer_scales, ptr(self.status), stream))
         dist.all_reduce(self.token, group=self.group)  # every rank's stores are done and visible after this
         return EPResult(self.rows, self.scales, self.local_offsets, self.cnt, -1, -1)
+
+    def expert_output_buffer(self) -> torch.Tensor:
+        """[max_recv_rows, H] bf16 in symmetric memory: the experts of this rank
+        write their outputs here, row i for received row i, before ``combine``."""
+        if getattr(self, "y", None) is None:
+            import torch.distributed._symmetric_memory as symm_mem
+            H = self.sess.H
+            self.y_buf = symm_mem.empty(self.max_rows * H, dtype=torch.bfloat16, device=self.buf.device)
+            self.y_hdl = symm_mem.rendezvous(self.y_buf, self.group)
+            self.peer_y = (ctypes.c_void_p * self.world)(*[int(p) for p in self.y_hdl.buffer_ptrs])
+            self.y = self.y_buf.view(self.max_rows, H)
+        return self.y
+
+    def combine(self, result=None, shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """out[t] = shared[t] + sum_k w[t,k] * y_owner[row of (t,k)]: the return
+        exchange and the un-permute in one kernel that pulls each row from the
+        rank that owns its expert (``expert_output_buffer`` there) over NVLink.
+        Call on every rank (collective): a one-element all-reduce before the
+        kernel orders it after every rank's expert outputs, one after it keeps the
+        buffers from being overwritten while a peer still reads them."""
+        r = result if result is not None else self.sess.result()
+        self.expert_output_buffer()
+        T, K, H, E = self.sess.T, self.sess.K, self.sess.H, self.sess.E
+        dev = self.buf.device
+        out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
+        dist.all_reduce(self.token, group=self.group)
+        stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+        def ptr(t):
+            return None if t is None else ctypes.c_void_p(t.data_ptr())
+        sh = None if shared is None else shared.reshape(T, H).contiguous()
+        _cabi.check(_cabi.lib().moe_rd_ep_combine(
+            T, H, K, E, self.world, self.peer_y, ptr(r.expert_ids), ptr(r.inverse_perm), ptr(r.combine_weights),
+            ptr(r.offsets), ptr(self.dest_base), ptr(sh), ptr(out), stream))
+        dist.all_reduce(self.token, group=self.group)
+        return out

@@ -248,6 +248,26 @@ int moe_rd_route_dispatch_timed(const moe_rd_params* p, const moe_rd_buffers* b,
 int moe_rd_read_status(const void* workspace, void* stream, int32_t status[8]);
 
 /*
+ * Expert-parallel weighted combine: the return path of moe_rd_ep_scatter and the
+ * un-permute in one kernel.  The expert outputs stay on the ranks that own the
+ * experts, in buffers laid out like the dispatch's receive buffers
+ * (peer_y[d] = rank d's [rows, H] bf16 output, mapped into this process); the
+ * row of pair (t,k), expert e = expert_ids[t,k], is row
+ * dest_base[e] + (inverse_perm[t,k] - offsets[e]) of peer_y[e / (E / world)]
+ * (dest_base from moe_rd_ep_plan) and is read from there with 16-byte loads over
+ * NVLink.  Arithmetic as moe_rd_combine.  The caller orders the kernel after
+ * every rank's outputs are written (a barrier on the stream) and keeps the
+ * buffers alive until every rank's kernel has finished.  The reference has no
+ * counterpart (single GPU); it is the second half of the exchange of its
+ * sharded_rows.py precedent.
+ */
+int moe_rd_ep_combine(int64_t T, int32_t H, int32_t K, int32_t E, int32_t world,
+                      const void* const* peer_y, const int32_t* expert_ids,
+                      const int32_t* inverse_perm, const float* combine_weights,
+                      const int32_t* offsets, const int32_t* dest_base, const void* shared,
+                      void* out, void* stream);
+
+/*
  * One group of a grouped (ragged) expert GEMM  D[m,n] = A[m,k] * B_e : what
  * plan_kernel of the reference builds per expert on the device from the routed
  * offsets (moe_gemm.cu:613-638: problem shape, A / B / D pointers, leading

@@ -1,4 +1,5 @@
-"""Expert-parallel dispatch on real GPUs (needs >= 2): every rank routes its
+"""Expert-parallel dispatch (and, for the fused form, the combine that pulls
+rows back) on real GPUs (needs >= 2): every rank routes its
 own seeded tokens, the ranks exchange counts, rows and scales over NCCL, and
 each rank's expert-major buffer must equal, bit for bit, the single-process
 statement of the exchange in the CPU oracle (fp8 rows and scales; tensor-core
@@ -70,6 +71,20 @@ def _worker(rank, world, port, T0, H, mode, q):
         np.testing.assert_array_equal(out.rows[:n].cpu().numpy(), ref["rows"])
         np.testing.assert_array_equal(out.scales[:n].cpu().numpy().view(np.uint32), ref["scales"].view(np.uint32))
         assert int(ep.status[0].item()) == 0
+        if fused:
+            # Return path: every owner turns its received fp8 bytes into bf16 "expert
+            # outputs"; each source rank pulls its rows back over NVLink and combines
+            # them.  Expected: the local combine of this rank's own quantised rows.
+            y = ep.expert_output_buffer()
+            y[:n] = out.rows[:n].to(torch.float32).to(torch.bfloat16)
+            got = ep.combine()
+            got = ep.combine()  # twice: the barriers keep the buffers consistent
+            torch.cuda.synchronize()
+            mine = per[rank]
+            y_local = torch.from_numpy(mine["permuted"].astype(np.float32)).to(torch.bfloat16)
+            y_bits = y_local.view(torch.int16).numpy().view(np.uint16)
+            ref_out = cpu_oracle.combine(y_bits, mine["inverse_perm"], mine["combine_weights"])
+            np.testing.assert_array_equal(got.cpu().view(torch.int16).numpy().view(np.uint16), ref_out)
         dist.barrier()
         dist.destroy_process_group()
         q.put((rank, "ok"))
