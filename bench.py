@@ -460,6 +460,70 @@ def run_combine(args):
         "gpu_launches": args.steps}), flush=True)
 
 
+def run_combine_ep(args, rank, world, local_rank):
+    """`--op combine` at N > 1: the expert-parallel combine (every rank pulls its pairs' expert outputs from
+    the owning ranks over NVLink inside the combine kernel).  Routing and the dispatch run once, untimed, to
+    fix the mapping; a step is one collective `combine` (barrier, kernel, barrier)."""
+    import torch
+    import torch.distributed as dist
+    from moe_rd import workloads
+    from moe_rd.runtime import Session
+    from moe_rd.ep import ExpertParallelFused
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    name = "c5"
+    spec = workloads.SPECS[name]
+    T, H, E, K = spec["T"], spec["H"], spec["E"], spec["K"]
+    t, kw = workloads.make(name, rank=rank)
+    keys = ("score_fn", "bias_mode", "n_groups", "topk_groups", "group_topk", "renorm", "routed_scale", "capacity",
+            "rows_format")
+    sess = Session(T, H, E, K, device=dev, w_dtype=t["w"].dtype, scatter_impl="none",
+                   **{k: v for k, v in kw.items() if k in keys})
+    ep = ExpertParallelFused(sess)
+    x, w, b = t["x"].to(dev), t["w"].to(dev), t["bias"].to(dev)
+    sess.run(x, w, b)
+    out = ep.exchange(x)
+    y = ep.expert_output_buffer()
+    n = int(out.offsets[-1].item())
+    y[:n].normal_()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        ep.combine()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    dist.barrier()
+    for s_, e_ in ev:
+        flush.zero_()
+        s_.record()
+        ep.combine()
+        e_.record()
+    torch.cuda.synchronize()
+    ms = sum(s_.elapsed_time(e_) for s_, e_ in ev) / args.steps
+    offs = sess.offsets.cpu()
+    epr = E // world
+    remote_rows = int(offs[E]) - int(offs[(rank + 1) * epr] - offs[rank * epr])
+    red = torch.tensor([ms, float(remote_rows) * H * 2], dtype=torch.float64, device=dev)
+    dist.all_reduce(red, op=dist.ReduceOp.MAX)
+    ms, ingress = float(red[0]), float(red[1])
+    if rank == 0:
+        link = 770.0
+        gbs = ingress / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "combined_tokens_per_s", "value": world * T / (ms * 1e-3), "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
+            "config": {"workload": "c5 combine, expert parallel", "tokens_per_rank": T, "hidden": H, "top_k": K,
+                       "experts": E, "l2": "flushed by a 256 MiB device write between steps"},
+            "roofline": {"bound": "nvlink", "kernel": "combine_kernel<EP> (16-byte peer loads)", "achieved": gbs,
+                         "peak": link, "unit": "GB/s", "frac": gbs / link,
+                         "peak_kind": "measured peer copy per direction (900 nominal)", "traffic": None,
+                         "bytes_per_launch": ingress, "kernel_ms": ms},
+            "gpu_launches": args.steps}), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def main():
     # NCCL prints its version banner on stdout at this level; stdout carries the one JSON line
     if os.environ.get("NCCL_DEBUG", "").upper() == "VERSION":
@@ -479,7 +543,9 @@ def main():
     if world == 1 and args.gpus > 1:
         raise SystemExit("launch with torchrun for --gpus > 1 (one process per GPU)")
     if args.op == "combine":
-        if rank == 0:
+        if world > 1:
+            run_combine_ep(args, rank, world, local_rank)
+        elif rank == 0:
             run_combine(args)
         return
     if args.impl == "reference":
