@@ -239,7 +239,8 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         from moe_rd.ep import ExpertParallel, ExpertParallelFused
         ep = (ExpertParallelFused(sess, dist.group.WORLD,
-                                  bulk={"auto": None, "bulk": True, "simt": False}[args.scatter]) if fused
+                                  bulk={"auto": None, "bulk": True, "simt": False}[args.scatter],
+                                  sync=args.ep_sync) if fused
               else ExpertParallel(sess, dist.group.WORLD))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
@@ -480,7 +481,7 @@ def run_combine_ep(args, rank, world, local_rank):
             "rows_format")
     sess = Session(T, H, E, K, device=dev, w_dtype=t["w"].dtype, scatter_impl="none",
                    **{k: v for k, v in kw.items() if k in keys})
-    ep = ExpertParallelFused(sess)
+    ep = ExpertParallelFused(sess, sync=args.ep_sync)
     x, w, b = t["x"].to(dev), t["w"].to(dev), t["bias"].to(dev)
     sess.run(x, w, b)
     out = ep.exchange(x)
@@ -536,6 +537,8 @@ def main():
     ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--scatter", default="auto", choices=["auto", "simt", "bulk"])
     ap.add_argument("--op", default="route_dispatch", choices=["route_dispatch", "combine"])
+    ap.add_argument("--ep-sync", default="symm", choices=["symm", "nccl"],
+                    help="fused exchange: count exchange and barriers through symmetric memory, or NCCL collectives")
     ap.add_argument("--ep", default="fused", choices=["fused", "nccl"],
                     help="expert-parallel exchange at N > 1: one peer-store kernel, or NCCL all-to-all + reorder")
     args = ap.parse_args()

@@ -24,8 +24,7 @@ constexpr unsigned kFull = 0xffffffffu;
 // Workspace carving, computed identically by moe_rd_workspace_bytes and by
 // the call itself.  All offsets are multiples of 256 bytes.
 struct Workspace {
-  size_t status;       // int32[8]  device status block            } cleared by one
-  size_t ticket;       // int32[8]  scan ticket counter            } memset at the
+  size_t status;       // int32[8]  device status block            } cleared at the
   size_t tile_base;    // int32[E*ntiles] per-tile counts, scanned } start of a call
                        //           in place to bases
   size_t counts;       // int32[E]  pairs per expert before dropping }
@@ -67,7 +66,7 @@ cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, c
                               float* logits_out, int32_t* ids, int32_t* tile_base, int32_t* counts,
                               cudaStream_t s);
 cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                        int32_t* tile_base, int32_t* counts, int32_t* ticket, cudaStream_t s);
+                        int32_t* tile_base, int32_t* counts, cudaStream_t s);
 cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                            const int32_t* ids, const int32_t* tile_base, const int32_t* counts,
                            int32_t* status, int32_t* dense, cudaStream_t s,
@@ -85,7 +84,7 @@ void count_launch(int n = 1);
 // launch start early (its blocks then park in pdl_sync until this grid has
 // completed and its writes are visible) and itself waits for the previous grid
 // before it touches global memory.  This hides the launch latency between the
-// five short kernels of a call.  Without the launch attribute both
+// short kernels of a call.  Without the launch attribute both
 // instructions do nothing.
 __device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

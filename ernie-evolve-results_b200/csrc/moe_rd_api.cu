@@ -68,7 +68,6 @@ void carve(const moe_rd_params& p, const Plan& plan, bool need_logits, bool need
            Workspace* w) {
   size_t o = 0;
   w->status = o; o += 256;
-  w->ticket = o; o += 256;
   w->tile_base = o; o += up256((size_t)p.E * plan.ntiles * 4);
   w->counts = o; o += up256((size_t)p.E * 4);
   w->dense = o; o += 256;
@@ -233,13 +232,12 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   MOE_RD_CUDA(init_device_once());
   unsigned char* ws = static_cast<unsigned char*>(workspace);
   int32_t* status = reinterpret_cast<int32_t*>(ws + w.status);
-  int32_t* ticket = reinterpret_cast<int32_t*>(ws + w.ticket);
   int32_t* counts = reinterpret_cast<int32_t*>(ws + w.counts);
   float* logits = need_logits ? reinterpret_cast<float*>(ws + w.logits) : b->router_logits;
   int32_t* tile_base = reinterpret_cast<int32_t*>(ws + w.tile_base);
   int32_t* ids = need_ids ? reinterpret_cast<int32_t*>(ws + w.ids) : b->expert_ids;
 
-  // status block, ticket counter and the tile counts are adjacent: one clear.  The
+  // status block, the tile counts and the expert counts are adjacent: one clear.  The
   // tensor-core gate clears them itself (its epilogue warps are idle while the
   // first tiles load), which saves the separate memset node.
   const bool gate_clears = plan.gate == MOE_RD_GATE_UMMA && p->T > 0;
@@ -266,7 +264,7 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
       MOE_RD_CUDA(launch_route(*p, *b, plan, logits, ids, tile_base, counts, s));
   }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[2], s));
-  MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, ticket, s));
+  MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[3], s));
   MOE_RD_CUDA(launch_scatter(*p, *b, plan, ids, tile_base, counts, status,
                              reinterpret_cast<int32_t*>(ws + w.dense), s, ev ? ev[4] : nullptr));

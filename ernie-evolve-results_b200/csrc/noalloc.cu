@@ -44,7 +44,7 @@ extern "C" int moe_rd_route_dispatch_noalloc(const moe_rd_params* p, const moe_r
   const int rs = scratch_for_current_device(&scratch);
   if (rs != MOE_RD_OK) return rs;
   // The pipeline clears the part of the scratch that must start at zero (status
-  // block, scan ticket, tile counts) at the head of every call, so what an
+  // block, tile counts, expert counts) at the head of every call, so what an
   // earlier call left behind does not matter.
   return moe_rd_route_dispatch(p, b, scratch, (size_t)MOE_RD_NOALLOC_MAX_BYTES, stream);
 }

@@ -224,8 +224,7 @@ cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b,
 }
 
 cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                        int32_t* tile_base, int32_t* counts, int32_t* ticket, cudaStream_t s) {
-  (void)ticket;
+                        int32_t* tile_base, int32_t* counts, cudaStream_t s) {
   const cudaError_t e = launch_pdl(scan_kernel, dim3((unsigned)p.E), dim3(kScanThreads), 0, s,
                                    tile_base, (const int32_t*)counts, b.counts, b.offsets, p.E,
                                    plan.ntiles, p.capacity);

@@ -364,6 +364,20 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
   }
 }
 
+// Every rank writes its kept rows per expert into slot `rank` of every peer's
+// [world][E] table (peer stores of E ints each): the count exchange without a
+// library collective; a cross-rank barrier follows on the stream.
+struct PushArgs {
+  int32_t* peer_kept[kMaxWorld];
+};
+__global__ void ep_push_counts_kernel(const int32_t* __restrict__ offsets, int E, int rank, int world,
+                                      const PushArgs pa) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  const int kept = offsets[e + 1] - offsets[e];
+  for (int d = 0; d < world; ++d) pa.peer_kept[d][(size_t)rank * E + e] = kept;
+}
+
 }  // namespace
 
 int device_sms();
@@ -501,6 +515,22 @@ extern "C" int moe_rd_ep_plan(const int32_t* kept_all, int world, int rank, int 
     return MOE_RD_E_SHAPE;
   ep_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       kept_all, world, rank, E, max_rows, dest_base, cnt, local_offsets, status);
+  count_launch();
+  return cudaGetLastError() == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
+}
+
+extern "C" int moe_rd_ep_push_counts(const int32_t* offsets, int E, int rank, int world,
+                                     int32_t* const* peer_kept, void* stream) {
+  if (offsets == nullptr || peer_kept == nullptr) return MOE_RD_E_NULL;
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || E < 1 || E > kMaxE)
+    return MOE_RD_E_SHAPE;
+  PushArgs pa = {};
+  for (int d = 0; d < world; ++d) {
+    if (peer_kept[d] == nullptr) return MOE_RD_E_NULL;
+    pa.peer_kept[d] = peer_kept[d];
+  }
+  ep_push_counts_kernel<<<(E + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(offsets, E, rank,
+                                                                                         world, pa);
   count_launch();
   return cudaGetLastError() == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
 }

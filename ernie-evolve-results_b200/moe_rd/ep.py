@@ -122,12 +122,19 @@ class ExpertParallelFused:
     mapping) and are sized once for the worst case.  ``exchange`` synchronises
     nothing on the host: gather of counts (NCCL), plan kernel, scatter kernel,
     and a one-element all-reduce that orders every rank's stores before anyone
-    reads its buffer.
+    reads its buffer.  With ``sync="symm"`` (default) the counts are pushed
+    into the peers' tables by a small kernel and the two synchronisations are
+    symmetric-memory signal barriers instead of NCCL collectives.
     """
 
     def __init__(self, session, group=None, max_recv_rows: Optional[int] = None,
-                 bulk: Optional[bool] = None):
+                 bulk: Optional[bool] = None, sync: str = "symm"):
         import torch.distributed._symmetric_memory as symm_mem
+        if sync not in ("symm", "nccl"):
+            raise ValueError("sync must be 'symm' or 'nccl'")
+        # "symm": counts are pushed into the peers' tables by a small kernel and the ranks meet at
+        # symmetric-memory signal barriers; "nccl": all-gather and one-element all-reduces.
+        self.sync = sync
         # Whole-row bulk copies (cp.async.bulk through shared memory) measured ~7 % more NVLink
         # bandwidth than 16-byte stores; they need 16-byte aligned scale rows (H % 512 == 0).
         H = session.H
@@ -161,7 +168,10 @@ class ExpertParallelFused:
         self.rows = (rows_u8 if self.fp8 else rows_u8.view(torch.bfloat16)).view(self.max_rows, H)
         self.scales = (self.buf[rows_bytes: rows_bytes + self.max_rows * self.nb * 4].view(torch.float32)
                        .view(self.max_rows, self.nb)) if self.fp8 else None
-        self.kept_all = torch.empty((self.world, E), dtype=torch.int32, device=dev)
+        self.kept_buf = symm_mem.empty(self.world * E, dtype=torch.int32, device=dev)
+        self.kept_hdl = symm_mem.rendezvous(self.kept_buf, self.group)
+        self.peer_kept = (ctypes.c_void_p * self.world)(*[int(p) for p in self.kept_hdl.buffer_ptrs])
+        self.kept_all = self.kept_buf.view(self.world, E)
         self.dest_base = torch.empty(E, dtype=torch.int32, device=dev)
         self.cnt = torch.empty((self.world, self.epr), dtype=torch.int32, device=dev)
         self.local_offsets = torch.empty(self.epr + 1, dtype=torch.int32, device=dev)
@@ -171,15 +181,19 @@ class ExpertParallelFused:
     def exchange(self, x: torch.Tensor, result=None) -> EPResult:
         r = result if result is not None else self.sess.result()
         offs = r.offsets
-        kept = (offs[1:] - offs[:-1]).contiguous()
-        # also a barrier: nobody overwrites a buffer its owner may still be reading
-        dist.all_gather_into_tensor(self.kept_all, kept, group=self.group)
         dev = self.buf.device
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
         def ptr(t):
             return ctypes.c_void_p(t.data_ptr())
         L = _cabi.lib()
+        # the count exchange is also a barrier: nobody overwrites a buffer its owner may still be reading
+        if self.sync == "nccl":
+            kept = (offs[1:] - offs[:-1]).contiguous()
+            dist.all_gather_into_tensor(self.kept_all, kept, group=self.group)
+        else:
+            _cabi.check(L.moe_rd_ep_push_counts(ptr(offs), self.sess.E, self.rank, self.world, self.peer_kept, stream))
+            self.kept_hdl.barrier(channel=0)
         _cabi.check(L.moe_rd_ep_plan(ptr(self.kept_all), self.world, self.rank, self.sess.E, self.max_rows,
                                      ptr(self.dest_base), ptr(self.cnt), ptr(self.local_offsets), ptr(self.status),
                                      stream))
@@ -190,8 +204,14 @@ class ExpertParallelFused:
         _cabi.check(L.moe_rd_ep_scatter(ctypes.byref(params), ptr(x), ptr(r.expert_ids),
                                         ptr(r.inverse_perm), ptr(offs), ptr(self.dest_base), self.world,
                                         self.peer_rows, self.peer_scales, ptr(self.status), stream))
-        dist.all_reduce(self.token, group=self.group)  # every rank's stores are done and visible after this
+        self._barrier(1)  # every rank's stores are done and visible after this
         return EPResult(self.rows, self.scales, self.local_offsets, self.cnt, -1, -1)
+
+    def _barrier(self, channel: int) -> None:
+        if self.sync == "nccl":
+            dist.all_reduce(self.token, group=self.group)
+        else:
+            self.hdl.barrier(channel=channel)
 
     def expert_output_buffer(self) -> torch.Tensor:
         """[max_recv_rows, H] bf16 in symmetric memory: the experts of this rank
@@ -217,7 +237,7 @@ class ExpertParallelFused:
         T, K, H, E = self.sess.T, self.sess.K, self.sess.H, self.sess.E
         dev = self.buf.device
         out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-        dist.all_reduce(self.token, group=self.group)
+        self._barrier(2)
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
         def ptr(t):
@@ -226,5 +246,5 @@ class ExpertParallelFused:
         _cabi.check(_cabi.lib().moe_rd_ep_combine(
             T, H, K, E, self.world, self.peer_y, ptr(r.expert_ids), ptr(r.inverse_perm), ptr(r.combine_weights),
             ptr(r.offsets), ptr(self.dest_base), ptr(sh), ptr(out), stream))
-        dist.all_reduce(self.token, group=self.group)
+        self._barrier(3)
         return out

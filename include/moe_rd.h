@@ -248,6 +248,16 @@ int moe_rd_route_dispatch_timed(const moe_rd_params* p, const moe_rd_buffers* b,
 int moe_rd_read_status(const void* workspace, void* stream, int32_t status[8]);
 
 /*
+ * Count exchange of the expert-parallel dispatch without a library collective:
+ * writes kept[e] = offsets[e+1] - offsets[e] of this rank into row `rank` of
+ * every peer's [world][E] table (peer_kept[d] = rank d's table, mapped into
+ * this process).  The caller follows it with a cross-rank barrier on the stream
+ * and then calls moe_rd_ep_plan on its own table.
+ */
+int moe_rd_ep_push_counts(const int32_t* offsets, int E, int rank, int world,
+                          int32_t* const* peer_kept, void* stream);
+
+/*
  * Expert-parallel weighted combine: the return path of moe_rd_ep_scatter and the
  * un-permute in one kernel.  The expert outputs stay on the ranks that own the
  * experts, in buffers laid out like the dispatch's receive buffers
