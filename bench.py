@@ -537,7 +537,7 @@ def main():
     ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
     ap.add_argument("--scatter", default="auto", choices=["auto", "simt", "bulk"])
     ap.add_argument("--op", default="route_dispatch", choices=["route_dispatch", "combine"])
-    ap.add_argument("--ep-sync", default="symm", choices=["symm", "nccl"],
+    ap.add_argument("--ep-sync", default="nccl", choices=["symm", "nccl"],
                     help="fused exchange: count exchange and barriers through symmetric memory, or NCCL collectives")
     ap.add_argument("--ep", default="fused", choices=["fused", "nccl"],
                     help="expert-parallel exchange at N > 1: one peer-store kernel, or NCCL all-to-all + reorder")

@@ -47,8 +47,8 @@ def _worker(rank, world, port, T0, H, mode, q):
                        scatter_impl="none" if fused else "auto")
         cls = ExpertParallelFused if fused else ExpertParallel
         kwargs = dict(bulk=True) if mode == "fused_bulk" else {}
-        if mode == "fused_nccl_sync":
-            kwargs = dict(sync="nccl")
+        if mode == "fused_symm_sync":
+            kwargs = dict(sync="symm")
         ep = cls(sess, max_recv_rows=world * (T0 + 64 * world) * K, **kwargs)
         x, w, b = t["x"].to(dev), t["w"].to(dev), t["bias"].to(dev)
         for _ in range(2):  # twice: buffers are reused
@@ -96,7 +96,7 @@ def _worker(rank, world, port, T0, H, mode, q):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least 2 GPUs")
-@pytest.mark.parametrize("mode", ["nccl", "fused", "fused_bulk", "fused_nccl_sync"])
+@pytest.mark.parametrize("mode", ["nccl", "fused", "fused_bulk", "fused_symm_sync"])
 def test_expert_parallel_exchange_matches_oracle(mode):
     import torch.multiprocessing as mp
     world = min(torch.cuda.device_count(), 4)
