@@ -63,7 +63,7 @@ cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b,
                                 float* logits_out, int32_t* ids, int32_t* tile_base,
                                 int32_t* counts, cudaStream_t s);
 cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                              float* logits_out, int32_t* ids, int32_t* tile_base, int32_t* counts,
+                              float* logits_out, int32_t* ids, int32_t* tile_base, int32_t* counts, int32_t* ticket,
                               cudaStream_t s);
 cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                         int32_t* tile_base, int32_t* counts, cudaStream_t s);

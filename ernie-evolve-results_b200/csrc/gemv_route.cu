@@ -59,6 +59,11 @@ struct GemvArgs {
   float* logits_out;  // optional [T,E]
   int H;
   int w_layout;
+  // the scans of the counts, done by the last block to finish
+  int32_t* ticket;       // zeroed before the kernel
+  int32_t* offsets;      // [E+1]
+  int32_t* user_counts;  // [E] or null
+  int64_t capacity;
 };
 
 // Bytes of the staged fp32 weight: rows padded to whole 256-row chunks.
@@ -83,7 +88,7 @@ gemv_route_kernel(const GemvArgs g, const RouteArgs a) {
   pdl_sync();
   extern __shared__ __align__(16) unsigned char smem[];
   float* s_wf = reinterpret_cast<float*>(smem);
-  int* s_cnt = reinterpret_cast<int*>(smem + staged_w_bytes(g.H, EB));  // [32] block histogram
+  int* s_cnt = reinterpret_cast<int*>(smem + staged_w_bytes(g.H, EB));  // [32] block histogram, [32] = last-block flag
   if (threadIdx.x < 32) s_cnt[threadIdx.x] = 0;
   // read back as two 64-bit halves: each half is already a {W[he], W[ho]} pair
   const ulonglong2* s_w = reinterpret_cast<const ulonglong2*>(smem);
@@ -201,36 +206,115 @@ gemv_route_kernel(const GemvArgs g, const RouteArgs a) {
       }
     }
 
-    // lane value = even chain + odd chain; lanes are summed by the fixed tree;
-    // lane e keeps expert e, and the warp routes the token at once
+    // lane value = even chain + odd chain; lanes are summed by the fixed tree
+    if (TPW > 1 && a.n_groups <= 1) {
+      // all TPW tokens of the warp are routed at once: token i in lanes i*W..i*W+W-1
+      constexpr int W = 32 / TPW;
+      float zp = 0.0f;
 #pragma unroll
-    for (int i = 0; i < TPW; ++i) {
-      float mine = 0.0f;
+      for (int i = 0; i < TPW; ++i) {
 #pragma unroll
-      for (int e = 0; e < EB; ++e) {
-        float v = __fadd_rn(lo_of(acc[i][e]), hi_of(acc[i][e]));
+        for (int e = 0; e < EB; ++e) {
+          float v = __fadd_rn(lo_of(acc[i][e]), hi_of(acc[i][e]));
 #pragma unroll
-        for (int o = 16; o; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(kFull, v, o));
-        if (lane == e) mine = v;
-      }
-      const int64_t t = tb + i;
-      if (t < a.T) {  // warp-uniform
-        if (lane < a.E) {
-          if (g.logit_bias != nullptr) mine = __fadd_rn(mine, __ldg(g.logit_bias + lane));
-          if (g.logits_out != nullptr) g.logits_out[(size_t)t * a.E + lane] = mine;
-        } else {
-          mine = 0.0f;
+          for (int o = 16; o; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(kFull, v, o));
+          if (lane == i * W + e) zp = v;
         }
-        float z[1] = {mine};
-        int mysel;
-        float myw;
-        route_token<1, false>(a, z, lane, nullptr, mysel, myw);
-        publish_token(a, t, lane, mysel, myw, s_cnt);
+      }
+      const int e = lane & (W - 1);
+      const int64_t t = tb + lane / W;
+      const bool live = t < a.T;
+      if (live && e < a.E) {
+        if (g.logit_bias != nullptr) zp = __fadd_rn(zp, __ldg(g.logit_bias + e));
+        if (g.logits_out != nullptr) g.logits_out[(size_t)t * a.E + e] = zp;
+      }
+      int mysel;
+      float myw;
+      route_token_packed<W>(a, zp, lane, mysel, myw);
+      if (live) publish_token(a, t, e, mysel, myw, s_cnt);
+    } else {
+      // lane e keeps expert e, and the warp routes one token at a time
+#pragma unroll
+      for (int i = 0; i < TPW; ++i) {
+        float mine = 0.0f;
+#pragma unroll
+        for (int e = 0; e < EB; ++e) {
+          float v = __fadd_rn(lo_of(acc[i][e]), hi_of(acc[i][e]));
+#pragma unroll
+          for (int o = 16; o; o >>= 1) v = __fadd_rn(v, __shfl_xor_sync(kFull, v, o));
+          if (lane == e) mine = v;
+        }
+        const int64_t t = tb + i;
+        if (t < a.T) {  // warp-uniform
+          if (lane < a.E) {
+            if (g.logit_bias != nullptr) mine = __fadd_rn(mine, __ldg(g.logit_bias + lane));
+            if (g.logits_out != nullptr) g.logits_out[(size_t)t * a.E + lane] = mine;
+          } else {
+            mine = 0.0f;
+          }
+          float z[1] = {mine};
+          int mysel;
+          float myw;
+          route_token<1, false>(a, z, lane, nullptr, mysel, myw);
+          publish_token(a, t, lane, mysel, myw, s_cnt);
+        }
       }
     }
   }
   __syncthreads();
   flush_counts(a, s_cnt, kGemvThreads);
+
+  // ---- The last block to finish turns the counts into bases and offsets (with
+  // at most 32 experts this is a microsecond of work; a kernel of its own costs
+  // several).  Follows the scan part of offsets_kernel of the reference
+  // (kernel.cu:2074-2086).
+  int* s_last = s_cnt + 32;  // (the kernel's whole shared-memory budget is dynamic)
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) *s_last = atomicAdd(g.ticket, 1) == (int)gridDim.x - 1;
+  __syncthreads();
+  if (!*s_last) return;
+  __threadfence();
+  for (int e = warp; e < a.E; e += kGemvWarps) {
+    // exclusive scan, in place, of the expert's per-tile counts: a warp per expert,
+    // eight chunks of 32 tiles loaded at a time
+    volatile int32_t* col = a.tile_counts + (size_t)e * a.ntiles;
+    int carry = 0;
+    for (int base = 0; base < a.ntiles; base += 256) {
+      int v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = base + 32 * j + lane;
+        v[j] = i < a.ntiles ? col[i] : 0;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        int incl = v[j];
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const int n = __shfl_up_sync(kFull, incl, o);
+          if (lane >= o) incl += n;
+        }
+        const int i = base + 32 * j + lane;
+        if (i < a.ntiles) col[i] = carry + incl - v[j];
+        carry += __shfl_sync(kFull, incl, 31);
+      }
+    }
+  }
+  if (warp == 0) {
+    // offsets[e] = rows kept by the experts before e (E <= 32: one lane each)
+    int c = lane < a.E ? reinterpret_cast<volatile int32_t*>(a.counts)[lane] : 0;
+    if (lane < a.E && g.user_counts != nullptr) g.user_counts[lane] = c;
+    if (g.capacity > 0 && (int64_t)c > g.capacity) c = (int)g.capacity;
+    int incl = c;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(kFull, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane < a.E) g.offsets[lane] = incl - c;
+    if (lane == a.E - 1) g.offsets[a.E] = incl;
+  }
 }
 
 int pick_eb(int E) { return E <= 8 ? 8 : E <= 16 ? 16 : 32; }
@@ -241,7 +325,7 @@ cudaError_t launch_t(const moe_rd_params& p, const GemvArgs& g, const RouteArgs&
   constexpr int TPW = GemvShape<EB>::TPW;
   constexpr int kGemvThreads = GemvShape<EB>::THREADS;
   constexpr int kGemvWarps = kGemvThreads / 32;
-  const size_t smem = staged_w_bytes(p.H, EB) + 128;
+  const size_t smem = staged_w_bytes(p.H, EB) + 256;
   const int64_t units = (p.T + TPW - 1) / TPW;
   const int64_t need = (units + kGemvWarps - 1) / kGemvWarps;
   const int64_t cap = device_sms();  // one block per SM (it fills the register file)
@@ -256,13 +340,17 @@ cudaError_t launch_t(const moe_rd_params& p, const GemvArgs& g, const RouteArgs&
 
 bool gemv_eligible(const moe_rd_params& p) {
   if (p.E > 32 || p.T <= 0) return false;
-  return staged_w_bytes(p.H, pick_eb(p.E)) + 128 <= (size_t)kMaxDynSmem;
+  return staged_w_bytes(p.H, pick_eb(p.E)) + 256 <= (size_t)kMaxDynSmem;
 }
 
 cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                               float* logits_out, int32_t* ids, int32_t* tile_base, int32_t* counts,
-                              cudaStream_t s) {
+                              int32_t* ticket, cudaStream_t s) {
   GemvArgs g;
+  g.ticket = ticket;
+  g.offsets = b.offsets;
+  g.user_counts = b.counts;
+  g.capacity = p.capacity;
   g.x = static_cast<const uint16_t*>(b.x);
   g.w = b.gate_w;
   g.logit_bias = b.logit_bias;

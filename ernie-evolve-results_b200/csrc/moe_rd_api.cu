@@ -255,7 +255,7 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[1], s));
   if (p->T > 0) {
     if (plan.gate == MOE_RD_GATE_GEMV)
-      MOE_RD_CUDA(launch_gemv_route(*p, *b, plan, b->router_logits, ids, tile_base, counts, s));
+      MOE_RD_CUDA(launch_gemv_route(*p, *b, plan, b->router_logits, ids, tile_base, counts, status + 16, s));
     else if (plan.gate == MOE_RD_GATE_UMMA)
       MOE_RD_CUDA(launch_route_splits(*p, *b, plan, reinterpret_cast<float*>(ws + w.partial),
                                       plan.ksplit, b->logit_bias, b->router_logits, ids, tile_base,
@@ -264,7 +264,8 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
       MOE_RD_CUDA(launch_route(*p, *b, plan, logits, ids, tile_base, counts, s));
   }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[2], s));
-  MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, s));
+  // the fused GEMV kernel scans in its last block; with T = 0 nothing ran and the scan kernel writes the zeros
+  if (plan.gate != MOE_RD_GATE_GEMV || p->T == 0) MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[3], s));
   MOE_RD_CUDA(launch_scatter(*p, *b, plan, ids, tile_base, counts, status,
                              reinterpret_cast<int32_t*>(ws + w.dense), s, ev ? ev[4] : nullptr));

@@ -294,6 +294,53 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)
   myw = __fmul_rn(wv, a.routed_scale);
 }
 
+// Several tokens per warp for few experts: token i of the warp lives in lanes
+// i*W .. i*W+W-1 (W = 8 or 16 lanes, E <= W), lane i*W+e holding the logit of
+// expert e.  Same arithmetic and order as route_token: the softmax sum of
+// route_token is the 32-lane tree over lanes that hold zeros beyond E, and adding
+// those zeros changes nothing, so the W-lane tree below gives the same bits.
+// No expert groups (callers use route_token when n_groups > 1).  On return lane
+// i*W+k (k < K) holds slot k of token i.
+template <int W>
+__device__ __forceinline__ void route_token_packed(const RouteArgs& a, float z, int lane, int& mysel,
+                                                   float& myw) {
+  const int e = lane & (W - 1);
+  const int base = lane & ~(W - 1);
+  const unsigned gmask = (W == 32) ? kFull : (((1u << W) - 1u) << base);
+  const bool valid = e < a.E;
+  float sc;
+  if (a.score_fn == MOE_RD_SCORE_SOFTMAX) {
+    const float m = ord_value(__reduce_max_sync(gmask, valid ? ord_key(z) : 0u));
+    const float p = valid ? exp_ieee(__fsub_rn(z, m)) : 0.0f;
+    float sum = p;
+#pragma unroll
+    for (int o = W / 2; o; o >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(gmask, sum, o));
+    sc = __fmul_rn(p, __frcp_rn(sum));
+  } else {
+    sc = valid ? __frcp_rn(__fadd_rn(1.0f, exp_ieee(-z))) : 0.0f;
+  }
+  float key = sc;
+  if (valid && a.select_bias != nullptr) key = __fadd_rn(key, __ldg(a.select_bias + e));
+  uint32_t ok = valid ? ord_key(key) : 0u;
+  float tot = 0.0f, myu = 0.0f;
+  mysel = 0;
+  for (int k = 0; k < a.K; ++k) {
+    const uint32_t mx = __reduce_max_sync(gmask, ok);
+    int win = (int)__reduce_min_sync(gmask, (unsigned)(ok == mx ? e : 0x7fffffff));
+    if (mx == 0u) win = 0x7fffffff;
+    win = min(max(win, 0), a.E - 1);
+    const float cand = a.weight_from_key ? ord_value(mx) : __shfl_sync(gmask, sc, base + win);
+    if (e == win) ok = 0u;
+    tot = __fadd_rn(tot, cand);
+    if (e == k) {
+      mysel = win;
+      myu = cand;
+    }
+  }
+  const float wv = a.renorm ? __fdiv_rn(myu, fmaxf(tot, a.norm_min)) : myu;
+  myw = __fmul_rn(wv, a.routed_scale);
+}
+
 // Lanes k < K publish slot k of token t: id, weight, one count for the
 // (expert, tile) cell, and one count in the block's shared histogram s_cnt[E]
 // (a popular expert would otherwise serialise tens of thousands of global

@@ -80,9 +80,9 @@ constexpr int kPosThreads = 256;
 // the per-chunk counts are prefix-summed per expert in pair order.
 __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionArgs a) {
   extern __shared__ __align__(16) uint16_t s_cc[];  // [chunks][E]
-  pdl_sync();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int nwarps = kPosThreads / 32;
+  constexpr int kRegChunks = 2;  // chunks per warp whose loads stay in registers (all of them for K <= 8)
   const int tile = blockIdx.x;
   const int64_t t0 = (int64_t)tile * kTile;
   const int ntok = (int)min((int64_t)kTile, a.T - t0);
@@ -90,14 +90,35 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
   const int nch = (P + 31) >> 5;
   const int32_t* ids = a.ids + (size_t)t0 * a.K;
   {
+    // independent of the kernels before: done while they finish
     uint32_t* z32 = reinterpret_cast<uint32_t*>(s_cc);
     const int nw = (nch * a.E + 1) >> 1;
     for (int i = tid; i < nw; i += kPosThreads) z32[i] = 0u;
   }
+  pdl_sync();
+  // Every global load of a pair - its expert, that expert's base in this tile and
+  // its first row - is issued here, before the shared-memory passes need them.
+  int e_reg[kRegChunks], tb_reg[kRegChunks], off_reg[kRegChunks];
+#pragma unroll
+  for (int k = 0; k < kRegChunks; ++k) {
+    const int p = (warp + k * nwarps) * 32 + lane;
+    const int e = p < P ? ids[p] : -1;
+    e_reg[k] = e;
+    const bool okay = e >= 0 && e < a.E;
+    tb_reg[k] = okay ? a.tile_base[(size_t)e * a.ntiles + tile] : 0;
+    off_reg[k] = okay ? a.offsets[e] : 0;
+  }
   __syncthreads();
-  for (int c = warp; c < nch; c += nwarps) {
+  for (int c = warp, k = 0; c < nch; c += nwarps, ++k) {
     const int p = c * 32 + lane;
-    int e = p < P ? ids[p] : -1;
+    int e = -1;
+    if (k < kRegChunks) {
+#pragma unroll
+      for (int kk = 0; kk < kRegChunks; ++kk)
+        if (kk == k) e = e_reg[kk];
+    } else {
+      e = p < P ? ids[p] : -1;
+    }
     if (e >= a.E) e = -1;
     const unsigned m = __match_any_sync(kFull, e);
     if (e >= 0 && (m & ((1u << lane) - 1u)) == 0u) s_cc[c * a.E + e] = (uint16_t)__popc(m);
@@ -112,9 +133,25 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
     }
   }
   __syncthreads();
-  for (int c = warp; c < nch; c += nwarps) {
+  for (int c = warp, k = 0; c < nch; c += nwarps, ++k) {
     const int p = c * 32 + lane;
-    const int e_raw = p < P ? ids[p] : -1;
+    int e_raw = -1, tb = 0, off = 0;
+    if (k < kRegChunks) {
+#pragma unroll
+      for (int kk = 0; kk < kRegChunks; ++kk) {
+        if (kk == k) {
+          e_raw = e_reg[kk];
+          tb = tb_reg[kk];
+          off = off_reg[kk];
+        }
+      }
+    } else {
+      e_raw = p < P ? ids[p] : -1;
+      if (e_raw >= 0 && e_raw < a.E) {
+        tb = a.tile_base[(size_t)e_raw * a.ntiles + tile];
+        off = a.offsets[e_raw];
+      }
+    }
     const int e = e_raw >= a.E ? -1 : e_raw;
     const unsigned m = __match_any_sync(kFull, e);
     if (p >= P) continue;
@@ -124,11 +161,10 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
     if (e < 0) {
       report(a.status, 1, e_raw, (int)s);
     } else {
-      const int64_t r = (int64_t)a.tile_base[(size_t)e * a.ntiles + tile] + s_cc[c * a.E + e] +
-                        __popc(m & ((1u << lane) - 1u));
+      const int64_t r = (int64_t)tb + s_cc[c * a.E + e] + __popc(m & ((1u << lane) - 1u));
       dropped = a.capacity > 0 && r >= a.capacity;
       if (!dropped) {
-        const int64_t q = (int64_t)a.offsets[e] + r;
+        const int64_t q = (int64_t)off + r;
         if (q < 0 || q >= a.out_rows)
           report(a.status, 2, (int)q, (int)s);
         else

@@ -195,7 +195,7 @@ def test_device_status_stays_clean_and_launches_are_counted():
     before = _cabi.launch_count()
     t, kw = workloads.make("c1")
     _util.run_gpu(t, kw)
-    assert _cabi.launch_count() - before >= 4  # fused gate+route, scan, positions, scatter
+    assert _cabi.launch_count() - before >= 3  # fused gate+route (scans in its last block), positions, scatter
 
 
 def test_round_trip_property_at_full_size():
