@@ -37,7 +37,7 @@ sys.path[:0] = [str(ROOT), str(ROOT / "ernie-evolve-results_b200")]
 # dram__bytes_read.sum + dram__bytes_write.sum of one scatter_kernel launch at the full workload, from the
 # ncu captures summarised in profiles/all_kernels_<workload>_*.md (below the algorithmic bytes: part of x is
 # still in L2 from the gate pass and the last written lines have not left L2 when the kernel ends).
-NCU_SCATTER_TRAFFIC = {"c2": 346.768e6, "c3": 1021.840e6, "c4": 547.956e6, "c5": 547.956e6}
+NCU_SCATTER_TRAFFIC = {"c2": 346.560e6, "c3": 1021.840e6, "c4": 545.160e6, "c5": 545.160e6}
 
 METRIC = "routed_tokens_per_s"
 UNIT = "tokens/s"
