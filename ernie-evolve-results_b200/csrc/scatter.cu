@@ -41,6 +41,9 @@ namespace {
 #ifndef MOE_RD_SC_PREFETCH_UNITS   // work units per warp whose x is requested before the grid dependency wait
 #define MOE_RD_SC_PREFETCH_UNITS 2
 #endif
+#ifndef MOE_RD_SC_FP8_LANE_ELEMS   // elements a lane quantises per work unit of an fp8 row: 16 or 32
+#define MOE_RD_SC_FP8_LANE_ELEMS 16
+#endif
 #ifndef MOE_RD_SC_STREAMING   // 1: st.global.cs (evict-first) for the row stores
 #define MOE_RD_SC_STREAMING 1
 #endif
@@ -290,9 +293,9 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
   // running.  x does not depend on it, so every warp asks L2 for the slices of x
   // it will read first and only then waits for the destinations.
   {
-    const int n16 = a.H >> 4;
-    const int upr = FMT == MOE_RD_ROWS_BF16 ? ((a.H >> 3) + 32 * kUV - 1) / (32 * kUV) : (n16 + 31) >> 5;
-    const int unit_bytes = FMT == MOE_RD_ROWS_BF16 ? 512 * kUV : 1024;
+    const int upr = FMT == MOE_RD_ROWS_BF16 ? ((a.H >> 3) + 32 * kUV - 1) / (32 * kUV)
+                                            : (a.H / MOE_RD_SC_FP8_LANE_ELEMS + 31) >> 5;
+    const int unit_bytes = FMT == MOE_RD_ROWS_BF16 ? 512 * kUV : 64 * MOE_RD_SC_FP8_LANE_ELEMS;
     const int row_bytes = a.H * 2;
     UnitWalk pw(w0, W, upr);
     for (int n = 0; n < MOE_RD_SC_PREFETCH_UNITS && pw.t < a.T; ++n, pw.next()) {
@@ -345,6 +348,68 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
       }
     }
   } else {
+#if MOE_RD_SC_FP8_LANE_ELEMS == 32
+    // unit = 1024 elements (eight 128-element scale blocks): 32 elements = four
+    // 16-byte loads per lane, 4 lanes per scale block, two 16-byte stores per lane
+    // and destination
+    const int n32 = a.H >> 5;
+    const int nb = a.H >> 7;
+    const int upr = (n32 + 31) >> 5;
+    const uint4* x4 = reinterpret_cast<const uint4*>(a.x);
+    UnitWalk wk(w0, W, upr);
+    for (; wk.t < a.T; wk.next()) {
+      const int64_t t = a.T - 1 - wk.t;  // last rows first (see above)
+      const int v = wk.c * 32 + lane;
+      const bool act = v < n32;
+      uint4 x0 = make_uint4(0, 0, 0, 0), x1 = x0, x2 = x0, x3 = x0;
+      if (act) {
+        const uint4* src = x4 + (size_t)t * (n32 * 4) + 4 * v;
+        x0 = __ldg(src);
+        x1 = __ldg(src + 1);
+        x2 = __ldg(src + 2);
+        x3 = __ldg(src + 3);
+      }
+      int qv[8];
+#pragma unroll
+      for (int k = 0; k < 8; ++k)
+        qv[k] = k < a.K ? __ldg(a.inverse_perm + (size_t)t * a.K + k) : -1;
+      float am = fmaxf(fmaxf(amax8(x0), amax8(x1)), fmaxf(amax8(x2), amax8(x3)));
+      am = fmaxf(am, __shfl_xor_sync(kFull, am, 2));
+      am = fmaxf(am, __shfl_xor_sync(kFull, am, 1));
+      const float scale = __fmul_rn(fmaxf(am, 1e-30f), 1.0f / 448.0f);
+      const float inv = __frcp_rn(scale);  // correctly rounded: the bits of 1.0f / scale
+      uint4 q0, q1;
+      q0.x = quant4(x0.x, x0.y, inv);
+      q0.y = quant4(x0.z, x0.w, inv);
+      q0.z = quant4(x1.x, x1.y, inv);
+      q0.w = quant4(x1.z, x1.w, inv);
+      q1.x = quant4(x2.x, x2.y, inv);
+      q1.y = quant4(x2.z, x2.w, inv);
+      q1.z = quant4(x3.x, x3.y, inv);
+      q1.w = quant4(x3.z, x3.w, inv);
+      if (act) {
+#pragma unroll 1
+        for (int kb = 0; kb < a.K; kb += 8) {
+          if (kb) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              qv[k] = kb + k < a.K ? __ldg(a.inverse_perm + (size_t)t * a.K + kb + k) : -1;
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            void* rows;
+            float* scl;
+            int64_t r;
+            if (!resolve_dest<EP>(a, t, kb + k, qv[k], rows, scl, r)) continue;
+            uint4* d = reinterpret_cast<uint4*>(rows) + (size_t)r * (n32 * 2) + 2 * v;
+            store_row16(d, q0);
+            store_row16(d + 1, q1);
+            if ((lane & 3) == 0) scl[(size_t)r * nb + (v >> 2)] = scale;
+          }
+        }
+      }
+    }
+#else
     // unit = 512 elements (four 128-element scale blocks): 16 elements per lane,
     // 8 lanes per scale block
     const int n16 = a.H >> 4;
@@ -371,7 +436,7 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
       am = fmaxf(am, __shfl_xor_sync(kFull, am, 2));
       am = fmaxf(am, __shfl_xor_sync(kFull, am, 1));
       const float scale = __fmul_rn(fmaxf(am, 1e-30f), 1.0f / 448.0f);
-      const float inv = __fdiv_rn(1.0f, scale);
+      const float inv = __frcp_rn(scale);  // correctly rounded: the bits of 1.0f / scale
       uint4 q;
       q.x = quant4(lo.x, lo.y, inv);
       q.y = quant4(lo.z, lo.w, inv);
@@ -397,6 +462,7 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
         }
       }
     }
+#endif
   }
 }
 
@@ -478,7 +544,7 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   a.K = p.K;
   a.dense = (p.flags & MOE_RD_FLAG_SKIP_IDENTITY_ROWS) ? dense : nullptr;
   const bool fp8 = p.rows_format == MOE_RD_ROWS_FP8_E4M3_B128;
-  const int64_t upr = fp8 ? ((p.H >> 4) + 31) >> 5 : ((p.H >> 3) + 32 * kUV - 1) / (32 * kUV);
+  const int64_t upr = fp8 ? (p.H / MOE_RD_SC_FP8_LANE_ELEMS + 31) >> 5 : ((p.H >> 3) + 32 * kUV - 1) / (32 * kUV);
   const int64_t units = p.T * upr;
   const int64_t want = (units + kScatterWarps - 1) / kScatterWarps;
   const int64_t cap = (int64_t)device_sms() * MOE_RD_SC_BLOCKS_PER_SM;
@@ -613,7 +679,7 @@ extern "C" int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const in
     a.peer_scales[d] = fp8 ? peer_scales[d] : nullptr;
     if (fp8 && a.peer_scales[d] == nullptr) return MOE_RD_E_NULL;
   }
-  const int64_t upr = fp8 ? ((p->H >> 4) + 31) >> 5 : ((p->H >> 3) + 32 * kUV - 1) / (32 * kUV);
+  const int64_t upr = fp8 ? (p->H / MOE_RD_SC_FP8_LANE_ELEMS + 31) >> 5 : ((p->H >> 3) + 32 * kUV - 1) / (32 * kUV);
   const int64_t units = p->T * upr;
   const int64_t want = (units + kScatterWarps - 1) / kScatterWarps;
   const int64_t cap = (int64_t)device_sms() * MOE_RD_SC_BLOCKS_PER_SM;
