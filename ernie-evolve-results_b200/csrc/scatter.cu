@@ -44,6 +44,9 @@ namespace {
 #ifndef MOE_RD_SC_FP8_LANE_ELEMS   // elements a lane quantises per work unit of an fp8 row: 16 or 32
 #define MOE_RD_SC_FP8_LANE_ELEMS 16
 #endif
+#ifndef MOE_RD_SC_VECTOR_SCALES   // 1: the four scales of an fp8 work unit leave in one 16-byte store
+#define MOE_RD_SC_VECTOR_SCALES 0
+#endif
 #ifndef MOE_RD_SC_STREAMING   // 1: st.global.cs (evict-first) for the row stores
 #define MOE_RD_SC_STREAMING 1
 #endif
@@ -442,6 +445,17 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
       q.y = quant4(lo.z, lo.w, inv);
       q.z = quant4(hi.x, hi.y, inv);
       q.w = quant4(hi.z, hi.w, inv);
+      // the unit's four scales in one 16-byte store by lane 0 (instead of four
+      // 4-byte stores by four lanes) when the unit is whole and rows of scales
+      // are 16-byte aligned
+      const bool vec_scales = MOE_RD_SC_VECTOR_SCALES && (nb & 3) == 0 && wk.c * 4 + 4 <= nb;
+      float4 s4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      if (vec_scales) {
+        s4.x = __shfl_sync(kFull, scale, 0);
+        s4.y = __shfl_sync(kFull, scale, 8);
+        s4.z = __shfl_sync(kFull, scale, 16);
+        s4.w = __shfl_sync(kFull, scale, 24);
+      }
       if (act) {
 #pragma unroll 1
         for (int kb = 0; kb < a.K; kb += 8) {
@@ -457,7 +471,11 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
             int64_t r;
             if (!resolve_dest<EP>(a, t, kb + k, qv[k], rows, scl, r)) continue;
             store_row16(reinterpret_cast<uint4*>(rows) + (size_t)r * n16 + v, q);
-            if ((lane & 7) == 0) scl[(size_t)r * nb + (v >> 3)] = scale;
+            if (vec_scales) {
+              if (lane == 0) *reinterpret_cast<float4*>(scl + (size_t)r * nb + wk.c * 4) = s4;
+            } else if ((lane & 7) == 0) {
+              scl[(size_t)r * nb + (v >> 3)] = scale;
+            }
           }
         }
       }
