@@ -292,6 +292,22 @@ def run_ours(args, rank, world, local_rank):
     total_ms = float(total_ms.item())
     value = world * T * args.steps / (total_ms / 1e3)
 
+    # --- spread of the timed steps on this rank, and the same call with a warm L2 (no flush in between)
+    st = sorted(times)
+    pct = lambda q: st[min(len(st) - 1, max(0, int(round(q * (len(st) - 1)))))]  # noqa: E731
+    evw = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    barrier()
+    for s, e in evw:
+        s.record()
+        step()
+        e.record()
+    barrier()
+    warm = [s.elapsed_time(e) for s, e in evw]
+    timing = {"cold_l2_ms": {"mean": sum(times) / len(times), "median": statistics.median(times),
+                             "p10": pct(0.1), "p90": pct(0.9)},
+              "warm_l2_ms": {"mean": sum(warm) / len(warm), "median": statistics.median(warm)},
+              "note": "this rank's steps; value and ms_per_step use the cold-L2 mean, max over ranks"}
+
     # --- per-stage device times for the roofline of the dominant kernel (row scatter)
     stage = []
     for _ in range(min(args.steps, 10)):
@@ -410,6 +426,7 @@ def run_ours(args, rank, world, local_rank):
             "nvlink": nvlink,
             "clocks": clocks,
             "kept_rows": kept,
+            "timing": timing,
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
