@@ -104,7 +104,11 @@ scan_kernel(int32_t* __restrict__ tile_base, const int32_t* __restrict__ counts,
             int32_t* __restrict__ user_counts, int32_t* __restrict__ offsets, int E, int ntiles,
             int64_t capacity) {
   __shared__ int s_w[kScanThreads / 32];
-  pdl_sync();
+  // Wait first, then let the next kernel start: the positions kernel reads the
+  // routing kernel's ids before its own wait, which is safe only once this grid
+  // has seen the routing kernel complete.
+  pdl_wait();
+  pdl_trigger();
   const int e = blockIdx.x, tid = threadIdx.x;
   // rows kept by the experts before this one (and by this one, for offsets[E])
   int before = 0, mine = 0;

@@ -47,6 +47,9 @@ namespace {
 #ifndef MOE_RD_SC_VECTOR_SCALES   // 1: the four scales of an fp8 work unit leave in one 16-byte store
 #define MOE_RD_SC_VECTOR_SCALES 0
 #endif
+#ifndef MOE_RD_POS_EARLY_IDS   // 1: the positions kernel ranks pairs while the scan kernel still runs
+#define MOE_RD_POS_EARLY_IDS 1
+#endif
 #ifndef MOE_RD_SC_STREAMING   // 1: st.global.cs (evict-first) for the row stores
 #define MOE_RD_SC_STREAMING 1
 #endif
@@ -76,6 +79,7 @@ struct PositionArgs {
   int32_t* dense;            // [1+kMaxK] identity experts: number, first rows (or null)
   int64_t T, capacity, out_rows;
   int E, K, ntiles;
+  int early_ids;             // 1: a scan kernel precedes this one (see positions_kernel)
 };
 
 constexpr int kPosThreads = 256;
@@ -101,18 +105,26 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
     const int nw = (nch * a.E + 1) >> 1;
     for (int i = tid; i < nw; i += kPosThreads) z32[i] = 0u;
   }
-  pdl_sync();
-  // Every global load of a pair - its expert, that expert's base in this tile and
-  // its first row - is issued here, before the shared-memory passes need them.
+  // The ids come from the routing kernel, the tile bases and offsets from the
+  // scan kernel after it.  When a scan kernel precedes this one (early_ids), it
+  // lets this grid start only after it has itself seen the routing kernel
+  // complete, so the ids may be read - and the in-tile ranks computed - while the
+  // scan kernel is still running; only the last pass waits for it.
+  pdl_trigger();
+  if (!a.early_ids) pdl_wait();
   int e_reg[kRegChunks], tb_reg[kRegChunks], off_reg[kRegChunks];
 #pragma unroll
   for (int k = 0; k < kRegChunks; ++k) {
     const int p = (warp + k * nwarps) * 32 + lane;
     const int e = p < P ? ids[p] : -1;
     e_reg[k] = e;
-    const bool okay = e >= 0 && e < a.E;
-    tb_reg[k] = okay ? a.tile_base[(size_t)e * a.ntiles + tile] : 0;
-    off_reg[k] = okay ? a.offsets[e] : 0;
+    tb_reg[k] = 0;
+    off_reg[k] = 0;
+    if (!a.early_ids && e >= 0 && e < a.E) {
+      // no scan kernel to overlap with: every load is issued up front
+      tb_reg[k] = a.tile_base[(size_t)e * a.ntiles + tile];
+      off_reg[k] = a.offsets[e];
+    }
   }
   __syncthreads();
   for (int c = warp, k = 0; c < nch; c += nwarps, ++k) {
@@ -136,6 +148,17 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
       const int v = s_cc[c * a.E + e];
       s_cc[c * a.E + e] = (uint16_t)run;
       run += v;
+    }
+  }
+  if (a.early_ids) {
+    pdl_wait();
+#pragma unroll
+    for (int k = 0; k < kRegChunks; ++k) {
+      const int e = e_reg[k];
+      if (e >= 0 && e < a.E) {
+        tb_reg[k] = a.tile_base[(size_t)e * a.ntiles + tile];
+        off_reg[k] = a.offsets[e];
+      }
     }
   }
   __syncthreads();
@@ -541,6 +564,7 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   pa.E = p.E;
   pa.K = p.K;
   pa.ntiles = plan.ntiles;
+  pa.early_ids = (plan.gate != MOE_RD_GATE_GEMV && MOE_RD_POS_EARLY_IDS) ? 1 : 0;
   cudaError_t e = launch_pdl(positions_kernel, dim3((unsigned)plan.ntiles), dim3(kPosThreads),
                              positions_smem(p.K, p.E), s, pa);
   count_launch();
