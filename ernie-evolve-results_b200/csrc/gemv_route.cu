@@ -27,7 +27,13 @@ constexpr int kMaxDynSmem = 227 * 1024;
 // 2 * TPW * EB accumulator registers per lane.  (Two tokens per warp with 1024
 // threads spills at 64 registers and measured 35 % slower on E = 8.)
 template <int EB> struct GemvShape;
-template <> struct GemvShape<8> { static constexpr int TPW = 4, THREADS = 512; };
+#ifndef MOE_RD_GEMV8_TPW      // tokens per warp and threads per block of the E <= 8 kernel
+#define MOE_RD_GEMV8_TPW 4
+#endif
+#ifndef MOE_RD_GEMV8_THREADS
+#define MOE_RD_GEMV8_THREADS 512
+#endif
+template <> struct GemvShape<8> { static constexpr int TPW = MOE_RD_GEMV8_TPW, THREADS = MOE_RD_GEMV8_THREADS; };
 template <> struct GemvShape<16> { static constexpr int TPW = 2, THREADS = 512; };
 template <> struct GemvShape<32> { static constexpr int TPW = 1, THREADS = 512; };
 
