@@ -228,8 +228,8 @@ int moe_rd_combine(int64_t T, int32_t H, int32_t K, const void* y, const int32_t
  * Same work as moe_rd_route_dispatch, but with a CUDA event recorded on
  * `stream` between the stages; synchronises the stream and returns the device
  * time of each stage in milliseconds: stage_ms[0] gate product, [1] scoring /
- * top-k / expert histogram (with the fused GEMV gate the product is in here),
- * [2] scans, [3] positions, [4] row scatter.  For measurement only
+ * top-k / expert histogram (with the fused GEMV gate the product and the scans
+ * are in here), [2] scans, [3] positions, [4] row scatter.  For measurement only
  * (the reference's per-kernel figures come from an external profiler,
  * kernel.cu:865-890); it creates and destroys events, so keep it off hot paths.
  */
