@@ -32,8 +32,9 @@ struct Workspace {
   size_t zero_bytes;   // length of that cleared prefix
   size_t logits;       // float[T*E] when the caller passes no router_logits
   size_t ids;          // int32[T*K] when the caller passes no expert_ids
-  size_t wt;           // bf16[E*H]  gate weight in [E,H] order for the tensor-core gate
-  size_t partial;      // float[S*T*E] split-K partial logits of the tensor-core gate
+  size_t wt;           // bf16[N*H]  gate weight in [N,H] order for the tensor-core gate (N = E, or
+                       //            2E: hi rows then lo rows of an fp32 weight)
+  size_t partial;      // float[S*T*N] split-K partial logits of the tensor-core gate
   size_t total;
 };
 
@@ -44,6 +45,9 @@ struct Plan {
   int ksplit;      // split-K factor of the tensor-core gate
   int umma_mh;     // 128-token halves per CTA of the tensor-core gate (1 or 2)
   int umma_pair;   // 1: two-CTA tiles (cta_group::2), each CTA fetching half of every W tile
+  int umma_fold;   // 1: fp32 gate weight split into bf16 hi and lo rows; the product has 2E columns
+                   //    and logit e = column e + column E+e
+  int umma_n;      // columns of the tensor-core product: E, or 2E with umma_fold
 };
 
 int make_plan(const moe_rd_params& p, Plan* plan);

@@ -548,6 +548,58 @@ __global__ void __launch_bounds__(256) transpose_w_kernel(const uint16_t* __rest
   }
 }
 
+// fp32 gate weight -> two bf16 rows per expert, K-major: wpk[e][h] = hi = bf16(W[e,h])
+// and wpk[E + e][h] = lo = bf16(W[e,h] - hi), so that a bf16 product with 2E columns
+// followed by  z[e] = D[e] + D[E + e]  reproduces the fp32-weight product to about
+// 2^-17 relative per term (wsplit_kernel of the reference, kernel.cu:1786-1824, and
+// its fold at 1849-1851; the reference packs [H,2E], here the rows are K-major so
+// that the same tiles serve both weight layouts).  W - hi is exact in fp32.
+__device__ __forceinline__ void split_bf16(float v, uint16_t& hi, uint16_t& lo) {
+  const __nv_bfloat16 h = __float2bfloat16_rn(v);
+  const __nv_bfloat16 l = __float2bfloat16_rn(__fsub_rn(v, __bfloat162float(h)));
+  hi = __bfloat16_as_ushort(h);
+  lo = __bfloat16_as_ushort(l);
+}
+
+// W[E,H]: four hidden indices per thread.
+__global__ void __launch_bounds__(256) wsplit_eh_kernel(const float* __restrict__ w,
+                                                        uint16_t* __restrict__ wpk, int H, int E) {
+  const size_t n4 = (size_t)E * H / 4;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+    const float4 v = __ldg(reinterpret_cast<const float4*>(w) + i);
+    uint16_t h0, h1, h2, h3, l0, l1, l2, l3;
+    split_bf16(v.x, h0, l0);
+    split_bf16(v.y, h1, l1);
+    split_bf16(v.z, h2, l2);
+    split_bf16(v.w, h3, l3);
+    reinterpret_cast<uint2*>(wpk)[i] = make_uint2(h0 | ((uint32_t)h1 << 16), h2 | ((uint32_t)h3 << 16));
+    reinterpret_cast<uint2*>(wpk + (size_t)E * H)[i] =
+        make_uint2(l0 | ((uint32_t)l1 << 16), l2 | ((uint32_t)l3 << 16));
+  }
+}
+
+// W[H,E]: 32x32 tiles through shared memory.
+__global__ void __launch_bounds__(256) wsplit_he_kernel(const float* __restrict__ w,
+                                                        uint16_t* __restrict__ wpk, int H, int E) {
+  __shared__ float tile[32][33];
+  const int h0 = blockIdx.x * 32, e0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int r = ty; r < 32; r += 8) {
+    const int h = h0 + r, e = e0 + tx;
+    tile[r][tx] = (h < H && e < E) ? __ldg(w + (size_t)h * E + e) : 0.0f;
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    const int e = e0 + r, h = h0 + tx;
+    if (e < E && h < H) {
+      uint16_t hi, lo;
+      split_bf16(tile[tx][r], hi, lo);
+      wpk[(size_t)e * H + h] = hi;
+      wpk[(size_t)(E + e) * H + h] = lo;
+    }
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -612,11 +664,26 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
                              void* wt, float* partial, float* logits, int32_t* status,
                              void* zero, size_t zero_bytes, cudaStream_t s) {
   (void)logits;
+  const int N = plan.umma_n;  // columns of the product: E, or 2E (hi and lo rows of an fp32 weight)
   const uint16_t* w_eh = static_cast<const uint16_t*>(b.gate_w);
   // W[H,E] with whole blocks of 64 experts is consumed in place as an MN-major
   // operand; otherwise it is transposed to the K-major W^T[E,H] first.
-  const bool mn_major = p.w_layout == MOE_RD_W_LAYOUT_HE && p.E % (plan.umma_pair ? 128 : 64) == 0;
-  if (p.w_layout == MOE_RD_W_LAYOUT_HE && !mn_major) {
+  const bool mn_major = !plan.umma_fold && p.w_layout == MOE_RD_W_LAYOUT_HE && p.E % (plan.umma_pair ? 128 : 64) == 0;
+  if (plan.umma_fold) {
+    const float* wf = static_cast<const float*>(b.gate_w);
+    if (p.w_layout == MOE_RD_W_LAYOUT_EH) {
+      const size_t n4 = (size_t)p.E * p.H / 4;
+      const unsigned blocks = (unsigned)((n4 + 255) / 256 < 1184 ? (n4 + 255) / 256 : 1184);
+      wsplit_eh_kernel<<<blocks, 256, 0, s>>>(wf, static_cast<uint16_t*>(wt), p.H, p.E);
+    } else {
+      const dim3 grid((unsigned)((p.H + 31) / 32), (unsigned)((p.E + 31) / 32));
+      wsplit_he_kernel<<<grid, 256, 0, s>>>(wf, static_cast<uint16_t*>(wt), p.H, p.E);
+    }
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    w_eh = static_cast<const uint16_t*>(wt);
+  } else if (p.w_layout == MOE_RD_W_LAYOUT_HE && !mn_major) {
     const dim3 grid((unsigned)((p.H + 31) / 32), (unsigned)((p.E + 31) / 32));
     transpose_w_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(b.gate_w),
                                             static_cast<uint16_t*>(wt), p.H, p.E);
@@ -629,15 +696,15 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
   if (!make_map(&map_x, b.x, (uint64_t)p.T, (uint64_t)p.H, kBlockM)) return cudaErrorInvalidValue;
   const bool pair = plan.umma_pair != 0;
   // K-major W^T: one box holds the rows (experts) one CTA needs per block of H
-  const uint32_t wt_box_rows = (uint32_t)(pair ? p.E / 2 : p.E);
+  const uint32_t wt_box_rows = (uint32_t)(pair ? N / 2 : N);
   if (mn_major ? !make_map(&map_w, b.gate_w, (uint64_t)p.H, (uint64_t)p.E, 64u)
-               : !make_map(&map_w, w_eh, (uint64_t)p.E, (uint64_t)p.H, wt_box_rows))
+               : !make_map(&map_w, w_eh, (uint64_t)N, (uint64_t)p.H, wt_box_rows))
     return cudaErrorInvalidValue;
   UmmaArgs a;
   a.partial = partial;
   a.status = status;
   a.T = p.T;
-  a.E = p.E;
+  a.E = N;
   a.kblocks = p.H / kBlockK;
   a.ksplit = plan.ksplit;
   a.mh = pair ? 1 : plan.umma_mh;
@@ -645,11 +712,11 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
   a.zero = static_cast<uint4*>(zero);
   a.zero_vecs = (uint32_t)(zero_bytes / 16);
   int cols = 32;
-  while (cols < p.E * a.mh) cols <<= 1;
+  while (cols < N * a.mh) cols <<= 1;
   a.tmem_cols = cols;
-  const size_t staging = (size_t)kBlockM * (p.E * 4 + 16);  // the epilogue parks 128 rows in the ring
+  const size_t staging = (size_t)kBlockM * (N * 4 + 16);  // the epilogue parks 128 rows in the ring
   if (pair) {
-    const int stage = kBlockM * kBlockK * 2 + (p.E / 2) * kBlockK * 2;
+    const int stage = kBlockM * kBlockK * 2 + (N / 2) * kBlockK * 2;
     int st = MOE_RD_UMMA_SMEM_KB_ONE_CTA * 1024 / stage;
     a.stages = st > 8 ? 8 : (st < 2 ? 2 : st);
     if (staging > (size_t)a.stages * stage) return cudaErrorInvalidValue;
@@ -658,12 +725,12 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
     const size_t smem = (size_t)a.stages * stage + (2 * a.stages + 1) * 8 + 16 + 1024;
     gate_umma_pair_kernel<<<grid, kThreads, smem, s>>>(map_x, map_w, a);
   } else {
-    a.stages = pick_stages(p.E, a.mh);
-    if (staging > (size_t)a.stages * (a.mh * kBlockM * kBlockK * 2 + p.E * kBlockK * 2))
+    a.stages = pick_stages(N, a.mh);
+    if (staging > (size_t)a.stages * (a.mh * kBlockM * kBlockK * 2 + N * kBlockK * 2))
       return cudaErrorInvalidValue;
     const int tile = kBlockM * a.mh;
     const dim3 grid((unsigned)((p.T + tile - 1) / tile), (unsigned)plan.ksplit);
-    gate_umma_kernel<<<grid, kThreads, umma_smem_bytes(p.E, a.stages, a.mh), s>>>(map_x, map_w, a);
+    gate_umma_kernel<<<grid, kThreads, umma_smem_bytes(N, a.stages, a.mh), s>>>(map_x, map_w, a);
   }
   count_launch();
   return cudaGetLastError();

@@ -24,9 +24,13 @@ bool bulk_scatter_eligible(const moe_rd_params& p);
 
 static size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
 
+// Columns of the tensor-core product: an fp32 weight is split into bf16 hi and lo
+// rows (wsplit_kernel of the reference, kernel.cu:1786-1824), which doubles them.
+static int umma_columns(const moe_rd_params& p) { return p.w_dtype == MOE_RD_W_F32 ? 2 * p.E : p.E; }
+
 static bool umma_eligible(const moe_rd_params& p) {
-  return umma_available() && p.w_dtype == MOE_RD_W_BF16 && p.E >= 16 && p.E <= 256 && p.E % 16 == 0 && p.H % 64 == 0 &&
-         p.T > 0;
+  const int n = umma_columns(p);
+  return umma_available() && p.E >= 16 && n <= 256 && n % 16 == 0 && p.H % 64 == 0 && p.T > 0;
 }
 
 int make_plan(const moe_rd_params& p, Plan* plan) {
@@ -51,7 +55,7 @@ int make_plan(const moe_rd_params& p, Plan* plan) {
   if (gate == MOE_RD_GATE_UMMA) {
     // two 128-token halves per CTA share every weight tile (half the L2 reads of
     // W) once there are enough tokens to still fill the SMs
-    mh = (p.T >= 4096 && p.E <= 128) ? 2 : 1;  // at E = 256 it measured no faster and doubles the splits
+    mh = (p.T >= 4096 && umma_columns(p) <= 128) ? 2 : 1;  // at 256 columns it measured no faster and doubles the splits
     const int64_t mtiles = (p.T + 128 * mh - 1) / (128 * mh);
     const int kblocks = p.H / 64;
     while (ksplit < 8 && mtiles * ksplit * 2 <= 148 && kblocks / (ksplit * 2) >= 4) ksplit *= 2;
@@ -59,7 +63,9 @@ int make_plan(const moe_rd_params& p, Plan* plan) {
   plan->umma_mh = mh;
   // many experts: the W tiles dominate the bytes a CTA pulls in, and a pair of
   // CTAs can share them
-  plan->umma_pair = (gate == MOE_RD_GATE_UMMA && !one_cta && p.E > 128 && p.E % 32 == 0) ? 1 : 0;
+  plan->umma_fold = (gate == MOE_RD_GATE_UMMA && p.w_dtype == MOE_RD_W_F32) ? 1 : 0;
+  plan->umma_n = umma_columns(p);
+  plan->umma_pair = (gate == MOE_RD_GATE_UMMA && !one_cta && plan->umma_n > 128 && plan->umma_n % 32 == 0) ? 1 : 0;
   plan->ksplit = ksplit;
   return MOE_RD_OK;
 }
@@ -75,10 +81,10 @@ void carve(const moe_rd_params& p, const Plan& plan, bool need_logits, bool need
   w->logits = o; if (need_logits) o += up256((size_t)p.T * p.E * 4);
   w->ids = o; if (need_ids) o += up256((size_t)p.T * p.K * 4);
   w->wt = o;
-  if (plan.gate == MOE_RD_GATE_UMMA && p.w_layout == MOE_RD_W_LAYOUT_HE)
-    o += up256((size_t)p.E * p.H * 2);
+  if (plan.gate == MOE_RD_GATE_UMMA && (p.w_layout == MOE_RD_W_LAYOUT_HE || plan.umma_fold))
+    o += up256((size_t)plan.umma_n * p.H * 2);
   w->partial = o;
-  if (plan.gate == MOE_RD_GATE_UMMA) o += up256((size_t)plan.ksplit * p.T * p.E * 4);
+  if (plan.gate == MOE_RD_GATE_UMMA) o += up256((size_t)plan.ksplit * p.T * plan.umma_n * 4);
   w->total = o;
 }
 

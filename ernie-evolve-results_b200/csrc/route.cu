@@ -21,17 +21,22 @@ constexpr int kRouteWarps = kRouteThreads / 32;
 // tokens to work through, 2 when it has one or two.
 template <int EPL, bool FULL>
 __device__ __forceinline__ void load_logits(const RouteArgs& a, int64_t t, int lane, float (&z)[EPL]) {
-  const size_t row = (size_t)t * a.E;
+  const int ncol = a.fold ? 2 * a.E : a.E;
+  const size_t row = (size_t)t * ncol;
 #pragma unroll
   for (int i = 0; i < EPL; ++i) {
     const int e = lane + 32 * i;
     float v = 0.0f;
     if (FULL || e < a.E) {
-      v = __ldg(a.logits + row + e);
-      for (int sp = 1; sp < a.nsplit; ++sp)
-        v = __fadd_rn(v, __ldg(a.logits + (size_t)sp * a.T * a.E + row + e));
+      // splits in ascending order; with the hi/lo weight split each split contributes hi + lo
+      for (int sp = 0; sp < a.nsplit; ++sp) {
+        const float* src = a.logits + (size_t)sp * a.T * ncol + row + e;
+        float part = __ldg(src);
+        if (a.fold) part = __fadd_rn(part, __ldg(src + a.E));
+        v = sp == 0 ? part : __fadd_rn(v, part);
+      }
       if (a.logit_bias != nullptr) v = __fadd_rn(v, __ldg(a.logit_bias + e));
-      if (a.logits_out != nullptr) a.logits_out[row + e] = v;
+      if (a.logits_out != nullptr) a.logits_out[(size_t)t * a.E + e] = v;
     }
     z[i] = v;
   }
@@ -161,6 +166,7 @@ void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan
   a->logit_bias = nullptr;
   a->logits_out = nullptr;
   a->nsplit = 1;
+  a->fold = 0;
   a->select_bias = b.select_bias;
   a->ids = ids;
   a->weights = b.combine_weights;
@@ -193,6 +199,7 @@ cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b,
   RouteArgs a;
   fill_route_args(p, b, plan, partial, ids, tile_base, counts, &a);
   a.nsplit = nsplit;
+  a.fold = plan.gate == MOE_RD_GATE_UMMA ? plan.umma_fold : 0;
   a.logit_bias = logit_bias;
   a.logits_out = logits_out;
   // Three resident blocks of 512 threads per SM when every warp then still has

@@ -33,6 +33,8 @@ struct RouteArgs {
   const float* logit_bias;   // [E] added after the splits are summed, or null
   float* logits_out;         // [T,E] final logits for the caller, or null
   int nsplit;                // number of K-split partial products to add, in order
+  int fold;                  // 1: a row of `logits` has 2E columns (bf16 hi and lo parts of an fp32
+                             // gate weight) and logit e = column e + column E+e (kernel.cu:1849-1851)
   const float* select_bias;  // [E] or null
   int32_t* ids;              // [T,K]
   float* weights;            // [T,K]

@@ -12,6 +12,11 @@ c4  T=8192  H=7168 E=256 sigmoid + selection-only bias U(-0.1,0.1), 8 groups,
     keep top-4 groups by the sum of each group's top-2, top-8 experts, weights
     normalised and scaled by 2.5, fp8-e4m3 rows with one scale per 128 elements
 c5  c4 per rank (T=8192 tokens per rank), experts sharded over the ranks
+ref the reference kernel's own problem (kernel.cu:1582-1583, 4324, 4347): T=8192
+    H=8192 E=64 top-8, fp32 gate weight in [E,H] layout drawn randn/sqrt(H), softmax,
+    a randn correction bias added to the scores for selection AND kept in the
+    weights (kernel.cu:1865-1866, 1891, 1909; input draws as kernel.cu:1291-1300
+    describes them), bf16 rows
 """
 from __future__ import annotations
 
@@ -26,6 +31,7 @@ SPECS = {
     "c3": dict(T=32768, H=2048, E=128, K=8, w_dtype=torch.bfloat16, w_std=0.02, seed=1003),
     "c4": dict(T=8192, H=7168, E=256, K=8, w_dtype=torch.bfloat16, w_std=0.006, seed=1004),
     "c5": dict(T=8192, H=7168, E=256, K=8, w_dtype=torch.bfloat16, w_std=0.006, seed=1005),
+    "ref": dict(T=8192, H=8192, E=64, K=8, w_dtype=torch.float32, w_std=None, seed=1029),
 }
 
 
@@ -40,10 +46,15 @@ def make(name: str, *, T: Optional[int] = None, rank: int = 0, H: Optional[int] 
     H = s["H"] if H is None else H
     E, K = s["E"], s["K"]
     gw = torch.Generator(device="cpu").manual_seed(s["seed"])
-    w = (torch.randn(H, E, generator=gw, dtype=torch.float32) * s["w_std"]).to(s["w_dtype"])
+    w_std = s["w_std"] if s["w_std"] is not None else 1.0 / math.sqrt(H)
+    w = (torch.randn(H, E, generator=gw, dtype=torch.float32) * w_std).to(s["w_dtype"])
     bias = None
     kw = dict(top_k=K, w_layout="HE")
-    if name == "c3":
+    if name == "ref":
+        w = w.t().contiguous()  # [E,H], the reference's layout
+        bias = torch.randn(E, generator=gw, dtype=torch.float32)
+        kw.update(w_layout="EH", score_fn="softmax", bias_mode="select_and_weight", renorm=True)
+    elif name == "c3":
         r = torch.randperm(E, generator=gw).to(torch.float32) + 1.0
         bias = (2.0 * r.pow(-1.1)).to(torch.float32)
         kw.update(score_fn="softmax", bias_mode="logit", renorm=True,

@@ -41,10 +41,14 @@ enum { MOE_RD_W_F32 = 0, MOE_RD_W_BF16 = 1 };
 enum { MOE_RD_W_LAYOUT_HE = 0 /* [H,E] row-major */, MOE_RD_W_LAYOUT_EH = 1 /* [E,H] */ };
 enum { MOE_RD_ROWS_BF16 = 0, MOE_RD_ROWS_FP8_E4M3_B128 = 1 };
 enum {
-  MOE_RD_GATE_AUTO = 0,     /* E <= 32: fused warp GEMV; E >= 64 with bf16 weights: tcgen05;
-                               otherwise the SIMT product */
+  MOE_RD_GATE_AUTO = 0,     /* E <= 32: fused warp GEMV; E >= 64: tcgen05 where MOE_RD_GATE_UMMA is
+                               available; otherwise the SIMT product */
   MOE_RD_GATE_SIMT = 1,     /* fixed-order fp32 FMA product, any E (defines the logit bits) */
-  MOE_RD_GATE_UMMA = 2,     /* tcgen05/TMEM tiles fed by TMA (bf16 weights, E % 16 == 0, E <= 256) */
+  MOE_RD_GATE_UMMA = 2,     /* tcgen05/TMEM tiles fed by TMA.  bf16 weights: E % 16 == 0, E <= 256.
+                               fp32 weights: split per call into bf16 hi = bf16(W) and
+                               lo = bf16(W - hi) rows and folded as z = D[e] + D[E+e], which the
+                               reference does to get an fp32-weight product from a bf16 MMA
+                               (wsplit_kernel, kernel.cu:1786-1824, 1849-1851); E % 8 == 0, E <= 128 */
   MOE_RD_GATE_EXTERNAL = 3, /* logits supplied by the caller in router_logits */
   MOE_RD_GATE_GEMV = 4,     /* warp GEMV fused with scoring/top-k (E <= 32, weight fits in
                                shared memory); same logit bits as MOE_RD_GATE_SIMT */
