@@ -17,6 +17,7 @@
 namespace moe_rd {
 
 constexpr int kTile = 64;    // tokens per counting tile (granularity of the expert histogram)
+constexpr int kTileGroup = 32;  // counting tiles per group (second level of the histogram)
 constexpr int kMaxE = 256;
 constexpr int kMaxK = 32;
 constexpr unsigned kFull = 0xffffffffu;
@@ -28,6 +29,7 @@ struct Workspace {
   size_t tile_base;    // int32[E*ntiles] per-tile counts, scanned } start of a call
                        //           in place to bases
   size_t counts;       // int32[E]  pairs per expert before dropping }
+  size_t group_counts; // int32[groups*E] pairs per expert and group of kTileGroup tiles }
   size_t dense;        // int32[1+kMaxK] number and first rows of identity experts }
   size_t zero_bytes;   // length of that cleared prefix
   size_t logits;       // float[T*E] when the caller passes no router_logits
@@ -45,6 +47,9 @@ struct Plan {
   int ksplit;      // split-K factor of the tensor-core gate
   int umma_mh;     // 128-token halves per CTA of the tensor-core gate (1 or 2)
   int umma_pair;   // 1: two-CTA tiles (cta_group::2), each CTA fetching half of every W tile
+  int tile_major;  // 1: the routing kernel leaves pair counts per [tile][expert] and per [group of
+                   //    tiles][expert] and the positions kernel derives tile bases and offsets from
+                   //    them (no scan kernel); 0: counts per [expert][tile], scanned in place
   int umma_fold;   // 1: fp32 gate weight split into bf16 hi and lo rows; the product has 2E columns
                    //    and logit e = column e + column E+e
   int umma_n;      // columns of the tensor-core product: E, or 2E with umma_fold
@@ -61,11 +66,11 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
                              cudaStream_t s);
 cudaError_t launch_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                          const float* logits, int32_t* ids, int32_t* tile_base, int32_t* counts,
-                         cudaStream_t s);
+                         int32_t* group_counts, cudaStream_t s);
 cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                                 const float* partial, int nsplit, const float* logit_bias,
                                 float* logits_out, int32_t* ids, int32_t* tile_base,
-                                int32_t* counts, cudaStream_t s);
+                                int32_t* counts, int32_t* group_counts, cudaStream_t s);
 cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                               float* logits_out, int32_t* ids, int32_t* tile_base, int32_t* counts, int32_t* ticket,
                               cudaStream_t s);
@@ -73,7 +78,7 @@ cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const P
                         int32_t* tile_base, int32_t* counts, cudaStream_t s);
 cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                            const int32_t* ids, const int32_t* tile_base, const int32_t* counts,
-                           int32_t* status, int32_t* dense, cudaStream_t s,
+                           int32_t* status, int32_t* dense, const int32_t* group_counts, cudaStream_t s,
                            cudaEvent_t after_positions = nullptr);
 bool umma_available();
 bool gemv_eligible(const moe_rd_params& p);

@@ -67,6 +67,7 @@ int make_plan(const moe_rd_params& p, Plan* plan) {
   plan->umma_n = umma_columns(p);
   plan->umma_pair = (gate == MOE_RD_GATE_UMMA && !one_cta && plan->umma_n > 128 && plan->umma_n % 32 == 0) ? 1 : 0;
   plan->ksplit = ksplit;
+  plan->tile_major = (gate != MOE_RD_GATE_GEMV && p.T > 0) ? 1 : 0;
   return MOE_RD_OK;
 }
 
@@ -76,6 +77,7 @@ void carve(const moe_rd_params& p, const Plan& plan, bool need_logits, bool need
   w->status = o; o += 256;
   w->tile_base = o; o += up256((size_t)p.E * plan.ntiles * 4);
   w->counts = o; o += up256((size_t)p.E * 4);
+  w->group_counts = o; o += up256((size_t)p.E * ((plan.ntiles + kTileGroup - 1) / kTileGroup) * 4);
   w->dense = o; o += 256;
   w->zero_bytes = o;
   w->logits = o; if (need_logits) o += up256((size_t)p.T * p.E * 4);
@@ -241,6 +243,7 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   int32_t* counts = reinterpret_cast<int32_t*>(ws + w.counts);
   float* logits = need_logits ? reinterpret_cast<float*>(ws + w.logits) : b->router_logits;
   int32_t* tile_base = reinterpret_cast<int32_t*>(ws + w.tile_base);
+  int32_t* group_counts = reinterpret_cast<int32_t*>(ws + w.group_counts);
   int32_t* ids = need_ids ? reinterpret_cast<int32_t*>(ws + w.ids) : b->expert_ids;
 
   // status block, the tile counts and the expert counts are adjacent: one clear.  The
@@ -265,16 +268,18 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
     else if (plan.gate == MOE_RD_GATE_UMMA)
       MOE_RD_CUDA(launch_route_splits(*p, *b, plan, reinterpret_cast<float*>(ws + w.partial),
                                       plan.ksplit, b->logit_bias, b->router_logits, ids, tile_base,
-                                      counts, s));
+                                      counts, group_counts, s));
     else
-      MOE_RD_CUDA(launch_route(*p, *b, plan, logits, ids, tile_base, counts, s));
+      MOE_RD_CUDA(launch_route(*p, *b, plan, logits, ids, tile_base, counts, group_counts, s));
   }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[2], s));
-  // the fused GEMV kernel scans in its last block; with T = 0 nothing ran and the scan kernel writes the zeros
-  if (plan.gate != MOE_RD_GATE_GEMV || p->T == 0) MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, s));
+  // the fused GEMV kernel scans in its last block; after the routing kernel the positions kernel
+  // derives bases and offsets itself; with T = 0 nothing ran and the scan kernel writes the zeros
+  if (p->T == 0)
+    MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[3], s));
   MOE_RD_CUDA(launch_scatter(*p, *b, plan, ids, tile_base, counts, status,
-                             reinterpret_cast<int32_t*>(ws + w.dense), s, ev ? ev[4] : nullptr));
+                             reinterpret_cast<int32_t*>(ws + w.dense), group_counts, s, ev ? ev[4] : nullptr));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[5], s));
   return MOE_RD_OK;
 }

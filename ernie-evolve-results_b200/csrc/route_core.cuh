@@ -25,6 +25,9 @@
 #ifndef MOE_RD_ROUTE_SORTED
 #define MOE_RD_ROUTE_SORTED 1
 #endif
+#ifndef MOE_RD_ROUTE_THRESHOLD   // 1: find the K experts through a threshold and a short list instead of
+#define MOE_RD_ROUTE_THRESHOLD 0 //    rounds of arg-max (same results; measured no faster, see route_token)
+#endif
 
 namespace moe_rd {
 
@@ -40,6 +43,10 @@ struct RouteArgs {
   float* weights;            // [T,K]
   int32_t* tile_counts;      // [E][ntiles], zeroed before the kernel
   int32_t* counts;           // [E], zeroed before the kernel
+  int32_t* group_counts;     // null, or [ceil(ntiles/kTileGroup)][E] pairs per expert and group of
+                             // kTileGroup tiles, zeroed before the kernel; tile_counts is then laid out
+                             // [ntiles][E] and `counts` is left alone
+  int blocks_per_group;      // with group_counts: consecutive blocks that share a group of tiles
   int64_t T;
   int E, K, ntiles;
   int n_groups, topk_groups, group_topk;
@@ -68,9 +75,24 @@ __device__ __forceinline__ float ord_value(uint32_t k) {
 // every round broadcasting it out of a register picked by a chain of selects.
 // A selected key is removed by zeroing its image (0 = not eligible), so a round
 // costs one max pass, one index pass and one removal pass over the registers.
+//
+// s_cand: null, or kRouteCandWords words of shared memory owned by this warp.
+// Then the K experts are found without rounds where possible:
+//   1. every register row i (a slice of 32 consecutive experts, lane + 32*i) that
+//      still has eligible keys notes its q-th largest key, q = ceil(K / such rows);
+//      the smallest of these, tau, is a lower bound of the K-th largest key of the
+//      token, because at least K keys are >= tau;
+//   2. the keys >= tau (a dozen or so) are listed in expert order by ballot;
+//   3. lane c counts the listed keys that beat key c (larger, or equal and listed
+//      earlier, i.e. with a lower expert index): that count is its slot if < K.
+// "Larger key first, lower index on ties" is a total order, so this is the set
+// and order that the K rounds of arg-max produce.  If more than 32 keys reach
+// tau (long runs of equal keys) or fewer than K are eligible, the rounds decide.
+constexpr int kRouteCandWords = 3 * 32 + 2 * kMaxK;
+
 template <int EPL, bool FULL>
 __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)[EPL], int lane,
-                                            float* s_sc, int& mysel, float& myw) {
+                                            float* s_sc, int& mysel, float& myw, uint32_t* s_cand = nullptr) {
   float sc[EPL];
   uint32_t ok[EPL];  // ordered images of the selection keys; 0 = not eligible
   if (a.score_fn == MOE_RD_SCORE_SOFTMAX) {
@@ -102,11 +124,6 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)
     ok[i] = (FULL || e < a.E) ? ord_key(key) : 0u;
   }
   const bool staged = s_sc != nullptr && EPL > 1 && !a.weight_from_key;
-  if (staged) {
-    __syncwarp();  // the previous token's readers are done with s_sc
-#pragma unroll
-    for (int i = 0; i < EPL; ++i) s_sc[lane + 32 * i] = sc[i];
-  }
 
   if (a.n_groups > 1) {
     const int gs = a.E / a.n_groups;
@@ -210,6 +227,85 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)
 
   float tot = 0.0f, myu = 0.0f;
   mysel = 0;
+  if (MOE_RD_ROUTE_THRESHOLD && s_cand != nullptr && EPL > 1) {
+    // rows that still have eligible keys, and the number of keys each notes
+    unsigned rows = 0u;
+#pragma unroll
+    for (int i = 0; i < EPL; ++i)
+      if (__any_sync(kFull, ok[i] != 0u)) rows |= 1u << i;
+    const int nrows = __popc(rows);
+    const int q = nrows > 0 ? (a.K + nrows - 1) / nrows : 99;
+    if (q <= 4) {
+      uint32_t tau = 0xffffffffu;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        if ((rows >> i) & 1u) {
+          uint32_t v = ok[i], m = 0u;
+          for (int r = 0; r < q; ++r) {
+            m = __reduce_max_sync(kFull, v);
+            if (r + 1 < q) {
+              // take ONE instance of the maximum out (equal keys count separately)
+              const unsigned holders = __ballot_sync(kFull, v == m);
+              if (lane == __ffs(holders) - 1) v = 0u;
+            }
+          }
+          tau = min(tau, m);
+        }
+      }
+      unsigned b[EPL];
+      int n = 0;
+#pragma unroll
+      for (int i = 0; i < EPL; ++i) {
+        b[i] = __ballot_sync(kFull, ok[i] >= tau && ok[i] != 0u);
+        n += __popc(b[i]);
+      }
+      if (n <= 32 && n >= a.K) {
+        uint32_t* s_k = s_cand;                                      // [32] listed keys, in expert order
+        int* s_e = reinterpret_cast<int*>(s_cand + 32);              // [32] their experts
+        float* s_v = reinterpret_cast<float*>(s_cand + 64);          // [32] their unbiased scores
+        int* s_sel = reinterpret_cast<int*>(s_cand + 96);            // [K] slots
+        float* s_u = reinterpret_cast<float*>(s_cand + 96 + kMaxK);  // [K]
+        __syncwarp();  // the previous token's readers are done
+        const unsigned below = (1u << lane) - 1u;
+        int base = 0;
+#pragma unroll
+        for (int i = 0; i < EPL; ++i) {
+          if ((b[i] >> lane) & 1u) {
+            const int pos = base + __popc(b[i] & below);
+            s_k[pos] = ok[i];
+            s_e[pos] = lane + 32 * i;
+            s_v[pos] = sc[i];
+          }
+          base += __popc(b[i]);
+        }
+        __syncwarp();
+        const uint32_t k = lane < n ? s_k[lane] : 0u;
+        int rank = 0;
+        for (int c = 0; c < n; ++c) {
+          const uint32_t k2 = s_k[c];
+          rank += (k2 > k || (k2 == k && c < lane)) ? 1 : 0;
+        }
+        if (lane < n && rank < a.K) {
+          s_sel[rank] = s_e[lane];
+          s_u[rank] = a.weight_from_key ? ord_value(k) : s_v[lane];
+        }
+        __syncwarp();
+        if (lane < a.K) {
+          mysel = s_sel[lane];
+          myu = s_u[lane];
+        }
+        for (int kk = 0; kk < a.K; ++kk) tot = __fadd_rn(tot, __shfl_sync(kFull, myu, kk));
+        const float wq = a.renorm ? __fdiv_rn(myu, fmaxf(tot, a.norm_min)) : myu;
+        myw = __fmul_rn(wq, a.routed_scale);
+        return;
+      }
+    }
+  }
+  if (staged) {
+    __syncwarp();  // the previous token's readers are done with s_sc
+#pragma unroll
+    for (int i = 0; i < EPL; ++i) s_sc[lane + 32 * i] = sc[i];
+  }
   // With many registers per lane and many rounds it pays to sort each lane's
   // keys once (descending; odd-even transposition with a strict compare keeps
   // equal keys in index order) and then only look at the head of every lane.
@@ -353,16 +449,21 @@ __device__ __forceinline__ void publish_token(const RouteArgs& a, int64_t t, int
     const size_t s = (size_t)t * a.K + lane;
     a.ids[s] = mysel;
     a.weights[s] = myw;
-    atomicAdd(a.tile_counts + (size_t)mysel * a.ntiles + (int)(t / kTile), 1);
+    if (a.group_counts != nullptr)
+      atomicAdd(a.tile_counts + (size_t)(t / kTile) * a.E + mysel, 1);  // [tile][expert]
+    else
+      atomicAdd(a.tile_counts + (size_t)mysel * a.ntiles + (int)(t / kTile), 1);
     atomicAdd(s_cnt + mysel, 1);
   }
 }
 
-// Block-wide: add the shared histogram to counts[E].  Call after a barrier.
-__device__ __forceinline__ void flush_counts(const RouteArgs& a, const int* s_cnt, int nthreads) {
+// Block-wide: add the shared histogram to counts[E], or to row `group` of
+// group_counts.  Call after a barrier.
+__device__ __forceinline__ void flush_counts(const RouteArgs& a, const int* s_cnt, int nthreads, int group = 0) {
+  int32_t* dst = a.group_counts != nullptr ? a.group_counts + (size_t)group * a.E : a.counts;
   for (int e = threadIdx.x; e < a.E; e += nthreads) {
     const int v = s_cnt[e];
-    if (v) atomicAdd(a.counts + e, v);
+    if (v) atomicAdd(dst + e, v);
   }
 }
 

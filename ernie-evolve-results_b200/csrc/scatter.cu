@@ -67,15 +67,17 @@ __device__ __forceinline__ void store_row16(uint4* p, const uint4& v) {
 
 struct PositionArgs {
   const int32_t* ids;
-  const int32_t* tile_base;  // [E][ntiles], scanned
-  const int32_t* offsets;    // [E+1]
+  const int32_t* tile_base;  // scanned mode: [E][ntiles] tile bases; tile mode: [ntiles][E] raw counts
+  const int32_t* group_counts;  // tile mode: [groups][E] pairs per expert and group of kTileGroup tiles
+  int32_t* offsets;          // [E+1]: read (scanned mode) or written by block 0 (tile mode)
   int32_t* inverse_perm;
   uint8_t* drop_mask;
   int32_t* status;
   const float* weights;      // [T,K] combine weights (read for row_weight)
   int32_t* row_token;        // [out_rows] or null
   float* row_weight;         // [out_rows] or null
-  const int32_t* counts;     // [E] pairs per expert before dropping
+  const int32_t* counts;     // scanned mode: [E] pairs per expert before dropping
+  int32_t* user_counts;      // tile mode: [E] output of the same, or null
   int32_t* dense;            // [1+kMaxK] identity experts: number, first rows (or null)
   int64_t T, capacity, out_rows;
   int E, K, ntiles;
@@ -83,13 +85,25 @@ struct PositionArgs {
 };
 
 constexpr int kPosThreads = 256;
+static_assert(kMaxE <= kPosThreads, "tile mode keeps one expert per thread");
 
 // One block per tile of kTile tokens.  The rank of a pair inside its tile and
 // expert is the number of earlier pairs (flat index t*K+k) of the tile with the
 // same expert: every 32 consecutive pairs are counted with __match_any_sync and
 // the per-chunk counts are prefix-summed per expert in pair order.
+//
+// TILE (after the routing kernel of route.cu): there is no scan kernel; the block
+// derives what it needs from the raw counts itself, thread e for expert e, with
+// coalesced loads that are all in flight at once: the expert's total (sum of its
+// group counts), the pairs in the tiles before this one (group counts of the
+// groups before, plus the tile counts of this group's earlier tiles), and, by a
+// block-wide scan over the experts, offsets[e] = rows kept by the experts
+// before e (the scan part of offsets_kernel of the reference, kernel.cu:2074-2086).
+// Block 0 writes offsets[E+1] and the per-expert counts out.
+template <bool TILE>
 __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionArgs a) {
   extern __shared__ __align__(16) uint16_t s_cc[];  // [chunks][E]
+  __shared__ int s_off[TILE ? kMaxE : 1], s_tb[TILE ? kMaxE : 1], s_tot[TILE ? kMaxE : 1], s_w[kPosThreads / 32];
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   constexpr int nwarps = kPosThreads / 32;
   constexpr int kRegChunks = 2;  // chunks per warp whose loads stay in registers (all of them for K <= 8)
@@ -111,7 +125,7 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
   // complete, so the ids may be read - and the in-tile ranks computed - while the
   // scan kernel is still running; only the last pass waits for it.
   pdl_trigger();
-  if (!a.early_ids) pdl_wait();
+  if (TILE || !a.early_ids) pdl_wait();
   int e_reg[kRegChunks], tb_reg[kRegChunks], off_reg[kRegChunks];
 #pragma unroll
   for (int k = 0; k < kRegChunks; ++k) {
@@ -120,11 +134,66 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
     e_reg[k] = e;
     tb_reg[k] = 0;
     off_reg[k] = 0;
-    if (!a.early_ids && e >= 0 && e < a.E) {
+    if (!TILE && !a.early_ids && e >= 0 && e < a.E) {
       // no scan kernel to overlap with: every load is issued up front
       tb_reg[k] = a.tile_base[(size_t)e * a.ntiles + tile];
       off_reg[k] = a.offsets[e];
     }
+  }
+  if (TILE) {
+    // kMaxE <= kPosThreads: one expert per thread
+    const int e = tid;
+    int total = 0, base = 0;
+    if (e < a.E) {
+      const int ngroups = (a.ntiles + kTileGroup - 1) / kTileGroup;
+      const int g0 = tile / kTileGroup;
+      // the earlier tiles of this group: all loads are issued before the first add
+      int tv[kTileGroup - 1];
+      const int32_t* tc = a.tile_base + (size_t)g0 * kTileGroup * a.E + e;
+      const int nt = tile - g0 * kTileGroup;
+#pragma unroll
+      for (int j = 0; j < kTileGroup - 1; ++j) tv[j] = j < nt ? tc[(size_t)j * a.E] : 0;
+      for (int gb = 0; gb < ngroups; gb += 8) {
+        int gv[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) gv[j] = gb + j < ngroups ? a.group_counts[(size_t)(gb + j) * a.E + e] : 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          total += gv[j];
+          if (gb + j < g0) base += gv[j];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < kTileGroup - 1; ++j) base += tv[j];
+    }
+    int kept = total;
+    if (a.capacity > 0 && (int64_t)kept > a.capacity) kept = (int)a.capacity;
+    int incl = kept;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int n = __shfl_up_sync(kFull, incl, o);
+      if (lane >= o) incl += n;
+    }
+    if (lane == 31) s_w[warp] = incl;
+    __syncthreads();
+    int before = 0, all = 0;
+#pragma unroll
+    for (int w = 0; w < nwarps; ++w) {
+      const int v = s_w[w];
+      if (w < warp) before += v;
+      all += v;
+    }
+    const int off = before + incl - kept;
+    if (e < a.E) {
+      s_off[e] = off;
+      s_tb[e] = base;
+      s_tot[e] = total;
+      if (tile == 0) {
+        a.offsets[e] = off;
+        if (a.user_counts != nullptr) a.user_counts[e] = total;
+      }
+    }
+    if (tile == 0 && tid == 0) a.offsets[a.E] = all;
   }
   __syncthreads();
   for (int c = warp, k = 0; c < nch; c += nwarps, ++k) {
@@ -150,7 +219,7 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
       run += v;
     }
   }
-  if (a.early_ids) {
+  if (!TILE && a.early_ids) {
     pdl_wait();
 #pragma unroll
     for (int k = 0; k < kRegChunks; ++k) {
@@ -176,12 +245,16 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
       }
     } else {
       e_raw = p < P ? ids[p] : -1;
-      if (e_raw >= 0 && e_raw < a.E) {
+      if (!TILE && e_raw >= 0 && e_raw < a.E) {
         tb = a.tile_base[(size_t)e_raw * a.ntiles + tile];
         off = a.offsets[e_raw];
       }
     }
     const int e = e_raw >= a.E ? -1 : e_raw;
+    if (TILE && e >= 0) {
+      tb = s_tb[e];
+      off = s_off[e];
+    }
     const unsigned m = __match_any_sync(kFull, e);
     if (p >= P) continue;
     const size_t s = (size_t)t0 * a.K + p;
@@ -213,10 +286,11 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
     int n = 0;
     for (int e0 = 0; e0 < a.E; e0 += 32) {
       const int e = e0 + lane;
-      const bool is = e < a.E && (int64_t)a.counts[e] == a.T && (a.capacity == 0 || a.T <= a.capacity);
+      const int cnt = e < a.E ? (TILE ? s_tot[e] : a.counts[e]) : 0;
+      const bool is = e < a.E && (int64_t)cnt == a.T && (a.capacity == 0 || a.T <= a.capacity);
       const unsigned m = __ballot_sync(kFull, is);
       const int j = n + __popc(m & ((1u << lane) - 1u));
-      if (is && j < kMaxK) a.dense[1 + j] = a.offsets[e];
+      if (is && j < kMaxK) a.dense[1 + j] = TILE ? s_off[e] : a.offsets[e];
       n += __popc(m);
     }
     if (lane == 0) a.dense[0] = n < kMaxK ? n : kMaxK;
@@ -535,13 +609,16 @@ bool bulk_scatter_eligible(const moe_rd_params& p);
 size_t positions_smem(int K, int E) { return (size_t)((kTile * K + 31) / 32) * E * 2 + 16; }
 
 cudaError_t init_scatter_attributes() {
-  return cudaFuncSetAttribute(positions_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  cudaError_t e = cudaFuncSetAttribute(positions_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)positions_smem(kMaxK, kMaxE));
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(positions_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                               (int)positions_smem(kMaxK, kMaxE));
 }
 
 cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                            const int32_t* ids, const int32_t* tile_base, const int32_t* counts,
-                           int32_t* status, int32_t* dense, cudaStream_t s,
+                           int32_t* status, int32_t* dense, const int32_t* group_counts, cudaStream_t s,
                            cudaEvent_t after_positions) {
   if (p.T == 0) {
     return after_positions ? cudaEventRecord(after_positions, s) : cudaSuccess;
@@ -557,6 +634,8 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   pa.row_token = b.row_token;
   pa.row_weight = b.row_weight;
   pa.counts = counts;
+  pa.group_counts = group_counts;
+  pa.user_counts = b.counts;
   pa.dense = (p.flags & MOE_RD_FLAG_SKIP_IDENTITY_ROWS) ? dense : nullptr;
   pa.T = p.T;
   pa.capacity = p.capacity;
@@ -564,9 +643,11 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   pa.E = p.E;
   pa.K = p.K;
   pa.ntiles = plan.ntiles;
-  pa.early_ids = (plan.gate != MOE_RD_GATE_GEMV && MOE_RD_POS_EARLY_IDS) ? 1 : 0;
-  cudaError_t e = launch_pdl(positions_kernel, dim3((unsigned)plan.ntiles), dim3(kPosThreads),
-                             positions_smem(p.K, p.E), s, pa);
+  pa.early_ids = (plan.gate != MOE_RD_GATE_GEMV && !plan.tile_major && MOE_RD_POS_EARLY_IDS) ? 1 : 0;
+  cudaError_t e = plan.tile_major ? launch_pdl(positions_kernel<true>, dim3((unsigned)plan.ntiles),
+                                               dim3(kPosThreads), positions_smem(p.K, p.E), s, pa)
+                                  : launch_pdl(positions_kernel<false>, dim3((unsigned)plan.ntiles),
+                                               dim3(kPosThreads), positions_smem(p.K, p.E), s, pa);
   count_launch();
   if (e != cudaSuccess) return e;
   if (after_positions) {
