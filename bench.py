@@ -17,7 +17,10 @@ batch of seeded synthetic tokens.  Rank 0 prints ONE JSON line.
   device time, against the measured HBM copy bandwidth of this pool.
 * ``cpu_baseline`` / ``--impl reference``: the CPU oracle (a port of the
   reference's algorithm; the reference has no CPU implementation of this path)
-  on the box's host cores.
+  on all of the box's host cores.
+* ``other_workloads`` (N = 1): a few steps of the other single-GPU workloads, and
+  ``gate_vs_cublas``: the gate stage beside ``torch.mm`` (cuBLAS, bf16 x bf16 ->
+  fp32) on the same operands - a comparison leg, never on the product path.
 """
 from __future__ import annotations
 
@@ -34,9 +37,10 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path[:0] = [str(ROOT), str(ROOT / "ernie-evolve-results_b200")]
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one scatter_kernel launch at the full workload, from the
-# ncu captures summarised in profiles/all_kernels_<workload>_*.md (below the algorithmic bytes: part of x is
-# still in L2 from the gate pass and the last written lines have not left L2 when the kernel ends).
+# dram__bytes_read.sum + dram__bytes_write.sum of one scatter_kernel launch at the full workload, read once
+# from a stored ncu capture of that kernel (it is not re-measured by this script; the JSON line says so).
+# Below the algorithmic bytes: part of x is still in L2 from the gate pass and the last written lines have
+# not left L2 when the kernel ends.
 NCU_SCATTER_TRAFFIC = {"c2": 346.560e6, "c3": 1021.840e6, "c4": 545.160e6, "c5": 545.160e6}
 
 METRIC = "routed_tokens_per_s"
@@ -141,12 +145,13 @@ def time_cpu(name, ranks, budget_s=12.0, max_passes=3, T=None):
     from oracle import cpu_oracle
     from moe_rd import workloads
     cpu_oracle.lib()
+    cpu_oracle.set_threads(os.cpu_count() or 1)
     cores = cpu_oracle.max_threads()
     tensors, kw = [], None
     for r in range(ranks):
         t, kw = workloads.make(name, rank=r, T=T)
         tensors.append(t)
-    E = tensors[0]["w"].shape[1]
+    E = workloads.SPECS[name]["E"]
     Tn = tensors[0]["x"].shape[0]
     times = []
     t_start = time.perf_counter()
@@ -168,6 +173,8 @@ def run_reference(args, rank, world):
     spec = workloads.SPECS[name]
     from oracle import cpu_oracle
     cpu_oracle.lib()
+    # torch.distributed.run exports OMP_NUM_THREADS=1 to its workers: ask for every host core explicitly
+    cpu_oracle.set_threads(os.cpu_count() or 1)
     tensors, kw = [], None
     for r in range(world):
         t, kw = workloads.make(name, rank=r)
@@ -191,11 +198,16 @@ def run_reference(args, rank, world):
     total = sum(times)
     value = world * T * len(times) / total
     cores = cpu_oracle.max_threads()
+    cfg = workload_config(name, spec, world)
+    if T != spec["T"]:
+        # bounded sample: say what was really processed per rank
+        cfg["tokens_per_rank"] = T
+        cfg["sample_of_tokens_per_rank"] = spec["T"]
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / len(times),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
-        "config": workload_config(name, spec, world),
+        "config": cfg,
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"{len(times)} full passes of {name} ({world} x {T} tokens) on {cores} threads"},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -240,7 +252,7 @@ def run_ours(args, rank, world, local_rank):
         from moe_rd.ep import ExpertParallel, ExpertParallelFused
         ep = (ExpertParallelFused(sess, dist.group.WORLD,
                                   bulk={"auto": None, "bulk": True, "simt": False}[args.scatter],
-                                  sync=args.ep_sync) if fused
+                                  layout=args.ep_layout) if fused
               else ExpertParallel(sess, dist.group.WORLD))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
@@ -341,16 +353,28 @@ def run_ours(args, rank, world, local_rank):
         offs = sess.offsets.cpu()
         epr = E // world
         egress = float((int(offs[E]) - int(offs[(rank + 1) * epr] - offs[rank * epr])) * row_bytes)
-        red = torch.tensor([ex_ms, egress, op_ms], dtype=torch.float64, device=dev)
+        # rows this rank RECEIVES from the other ranks (routing can load the owners unevenly)
+        kept_me = (sess.offsets[1:] - sess.offsets[:-1]).to(torch.int64)
+        kept_all = [torch.empty_like(kept_me) for _ in range(world)]
+        dist.all_gather(kept_all, kept_me)
+        mine = slice(rank * epr, (rank + 1) * epr)
+        ingress = float(sum(int(k[mine].sum()) for r_, k in enumerate(kept_all) if r_ != rank) * row_bytes)
+        red = torch.tensor([ex_ms, egress, op_ms, ingress], dtype=torch.float64, device=dev)
         dist.all_reduce(red, op=dist.ReduceOp.MAX)
-        ex_ms, egress, step_ms = (float(v) for v in red)
+        ex_ms, egress, step_ms, ingress_max = (float(v) for v in red)
+        mean = torch.tensor([ingress], dtype=torch.float64, device=dev)
+        dist.all_reduce(mean, op=dist.ReduceOp.SUM)
+        ingress_mean = float(mean.item()) / world
         link_gbs = 770.0  # measured peer-copy bandwidth per direction per GPU on this pool (900 nominal)
-        roof_ms = max(egress / link_gbs / 1e6, op_bytes / peak / 1e6)
-        nvlink = {"egress_bytes_per_rank_max": egress, "exchange_ms": ex_ms,
-                  "exchange_gbs": egress / (ex_ms * 1e-3) / 1e9, "link_peak_gbs": link_gbs,
+        wire = max(egress, ingress_max)  # the busiest direction of the busiest rank bounds the exchange
+        roof_ms = max(wire / link_gbs / 1e6, op_bytes / peak / 1e6)
+        nvlink = {"egress_bytes_per_rank_max": egress, "ingress_bytes_per_rank_max": ingress_max,
+                  "ingress_bytes_per_rank_mean": ingress_mean, "exchange_ms": ex_ms,
+                  "exchange_gbs": wire / (ex_ms * 1e-3) / 1e9, "link_peak_gbs": link_gbs,
                   "link_peak_kind": "measured peer copy per direction (900 nominal)",
                   "roofline_ms": roof_ms, "step_ms": step_ms, "frac_of_roofline": roof_ms / step_ms,
-                  "frac_of_900": max(egress / 900.0 / 1e6, op_bytes / peak / 1e6) / step_ms, "mode": args.ep}
+                  "frac_of_900": max(wire / 900.0 / 1e6, op_bytes / peak / 1e6) / step_ms, "mode": args.ep,
+                  "layout": getattr(ep, "layout", None)}
     clocks = sampler.stop() if rank == 0 else None
     if fused:
         roofline = {"bound": "nvlink",
@@ -359,14 +383,17 @@ def run_ours(args, rank, world, local_rank):
                     "achieved": nvlink["exchange_gbs"], "peak": nvlink["link_peak_gbs"], "unit": "GB/s",
                     "frac": nvlink["exchange_gbs"] / nvlink["link_peak_gbs"],
                     "peak_kind": nvlink["link_peak_kind"], "traffic": None,
-                    "bytes_per_launch": nvlink["egress_bytes_per_rank_max"], "kernel_ms": nvlink["exchange_ms"],
+                    "bytes_per_launch": max(nvlink["egress_bytes_per_rank_max"], nvlink["ingress_bytes_per_rank_max"]),
+                    "kernel_ms": nvlink["exchange_ms"],
                     "stage_ms": stages, "whole_op": whole}
     else:
         scatter_gbs = scatter_bytes / (stage_ms[4] * 1e-3) / 1e9
         roofline = {
             "bound": "hbm", "kernel": "scatter_kernel", "achieved": scatter_gbs, "peak": peak, "unit": "GB/s",
             "frac": scatter_gbs / peak, "peak_kind": f"{peak_kind} HBM copy bandwidth",
-            "traffic": NCU_SCATTER_TRAFFIC.get(name), "bytes_per_launch": scatter_bytes,
+            "traffic": NCU_SCATTER_TRAFFIC.get(name),
+            "traffic_source": "stored ncu capture of scatter_kernel at this workload, not measured in this run",
+            "bytes_per_launch": scatter_bytes,
             "kernel_ms": stage_ms[4], "stage_ms": stages, "whole_op": whole,
         }
 
@@ -411,6 +438,11 @@ def run_ours(args, rank, world, local_rank):
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_value = world * T * e2e_steps / (float(e2e_ms.item()) / 1e3)
 
+    sweep = None
+    if world == 1 and not args.no_sweep:
+        del sess, x, x_in, x_host, host_out, outs
+        torch.cuda.empty_cache()
+        sweep = run_sweep(dev, flush, [n for n in ("c2", "c3", "ref") if n != name], peak)
     line = None
     if rank == 0:
         cpu = time_cpu(name, 1) if world == 1 else None
@@ -430,11 +462,94 @@ def run_ours(args, rank, world, local_rank):
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if sweep is not None:
+            line["other_workloads"] = sweep["other_workloads"]
+            line["gate_vs_cublas"] = sweep["gate_vs_cublas"]
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
     if line is not None:
         print(json.dumps(line), flush=True)
+
+
+def run_sweep(dev, flush, names, peak, steps=10):
+    """A few steps of other single-GPU workloads (device-timed, L2 flushed between steps), and for the
+    workloads whose gate runs on the tensor cores the gate stage beside cuBLAS on the same operands:
+    torch.mm of x [T,H] bf16 with the bf16 operand the gate kernel consumes ([H,E], or [H,2E] hi|lo columns
+    for an fp32 weight, the reference's own GEMM shape, kernel.cu:4327-4339), fp32 output."""
+    import torch
+    from moe_rd import workloads
+    from moe_rd.runtime import Session
+    other, cmp_ = {}, {}
+    for name in names + ["c4"]:
+        spec = workloads.SPECS[name]
+        T, H, E, K = spec["T"], spec["H"], spec["E"], spec["K"]
+        tensors, kw = workloads.make(name)
+        x, w = tensors["x"].to(dev), tensors["w"].to(dev)
+        bias = None if tensors["bias"] is None else tensors["bias"].to(dev)
+        sess = Session(T, H, E, K, device=dev, w_dtype=w.dtype, **session_kwargs(kw))
+        for _ in range(3):
+            flush.zero_()
+            sess.run(x, w, bias)
+        ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+        torch.cuda.synchronize()
+        for s_, e_ in ev:
+            flush.zero_()
+            s_.record()
+            sess.run(x, w, bias)
+            e_.record()
+        torch.cuda.synchronize()
+        sess.status()
+        ms = statistics.mean(s_.elapsed_time(e_) for s_, e_ in ev)
+        stage = []
+        for _ in range(5):
+            flush.zero_()
+            stage.append(sess.run_timed(x, w, bias))
+        st = [statistics.mean(v[i] for v in stage) for i in range(5)]
+        kept = int(sess.offsets[-1].item())
+        fp8 = kw.get("rows_format", "bf16") == "fp8"
+        nbytes = workloads.algorithmic_bytes(T, H, E, K, w_bytes=w.element_size(), fp8=fp8, kept_rows=kept)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        if name != "c4":  # c4 is the headline workload itself; it is here for the cuBLAS leg only
+            other[name] = {"ms_per_step": ms, "value": T / (ms * 1e-3), "unit": UNIT, "kept_rows": kept,
+                           "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac_of_measured": gbs / peak,
+                           "frac_of_8000": gbs / 8000.0,
+                           "stage_ms": {"gate": st[0], "route": st[1], "positions": st[3], "scatter": st[4]},
+                           "steps": steps}
+        if E >= 64:
+            if w.dtype == torch.float32:
+                wf = w if kw.get("w_layout", "HE") == "HE" else w.t()
+                hi = wf.to(torch.bfloat16)
+                lo = (wf - hi.to(torch.float32)).to(torch.bfloat16)
+                wb = torch.cat([hi, lo], dim=1).contiguous()
+            else:
+                wb = (w if kw.get("w_layout", "HE") == "HE" else w.t()).contiguous()
+            try:
+                mm = lambda: torch.mm(x, wb, out_dtype=torch.float32)  # noqa: E731
+                mm()
+                out_kind = "fp32"
+            except (TypeError, RuntimeError):
+                mm = lambda: torch.mm(x, wb)  # noqa: E731
+                out_kind = "bf16"
+            for _ in range(3):
+                mm()
+            evc = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+            torch.cuda.synchronize()
+            for s_, e_ in evc:
+                flush.zero_()
+                s_.record()
+                mm()
+                e_.record()
+            torch.cuda.synchronize()
+            cub = statistics.mean(s_.elapsed_time(e_) for s_, e_ in evc) * 1e3
+            cmp_[name] = {"shape": f"[{T},{H}]x[{H},{wb.shape[1]}]", "ours_us": st[0] * 1e3, "cublas_us": cub,
+                          "cublas_out": out_kind,
+                          "note": "both are CUDA-event pairs around the launch(es) with a cold L2; ours includes the "
+                                  "per-call weight split for fp32 weights and writes split-K partials"}
+            del wb
+        del sess, x, w
+        torch.cuda.empty_cache()
+    return {"other_workloads": other, "gate_vs_cublas": cmp_}
 
 
 def run_combine(args):
@@ -498,7 +613,7 @@ def run_combine_ep(args, rank, world, local_rank):
             "rows_format")
     sess = Session(T, H, E, K, device=dev, w_dtype=t["w"].dtype, scatter_impl="none",
                    **{k: v for k, v in kw.items() if k in keys})
-    ep = ExpertParallelFused(sess, sync=args.ep_sync)
+    ep = ExpertParallelFused(sess)
     x, w, b = t["x"].to(dev), t["w"].to(dev), t["bias"].to(dev)
     sess.run(x, w, b)
     out = ep.exchange(x)
@@ -551,11 +666,13 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5"])
+    ap.add_argument("--workload", default="c5", choices=["c1", "c2", "c3", "c4", "c5", "ref"])
+    ap.add_argument("--no-sweep", action="store_true",
+                    help="skip the other_workloads / gate_vs_cublas legs of the N = 1 line")
     ap.add_argument("--scatter", default="auto", choices=["auto", "simt", "bulk"])
     ap.add_argument("--op", default="route_dispatch", choices=["route_dispatch", "combine"])
-    ap.add_argument("--ep-sync", default="nccl", choices=["symm", "nccl"],
-                    help="fused exchange: count exchange and barriers through symmetric memory, or NCCL collectives")
+    ap.add_argument("--ep-layout", default=None, choices=["packed", "separate"],
+                    help="fused exchange, fp8 rows: scales after each row (one copy per pair) or in a buffer of their own")
     ap.add_argument("--ep", default="fused", choices=["fused", "nccl"],
                     help="expert-parallel exchange at N > 1: one peer-store kernel, or NCCL all-to-all + reorder")
     args = ap.parse_args()

@@ -43,11 +43,15 @@ struct CombineArgs {
   int epr;
 };
 
+// Row of pair (t,k) kept at local row pos; null when the pair has no row on its
+// owner (moe_rd_ep_plan found that the expert's rows do not fit there).
 template <bool EP>
 __device__ __forceinline__ const uint4* row_of(const CombineArgs& a, int64_t t, int k, int pos) {
   if (!EP) return a.y + (size_t)pos * a.nvec;
   const int e = __ldg(a.ids + (size_t)t * a.K + k);
-  const int64_t row = (int64_t)__ldg(a.dest_base + e) + (pos - __ldg(a.offsets + e));
+  const int db = __ldg(a.dest_base + e);
+  if (db < 0) return nullptr;
+  const int64_t row = (int64_t)db + (pos - __ldg(a.offsets + e));
   return a.peer_y[e / a.epr] + (size_t)row * a.nvec;
 }
 
@@ -67,8 +71,15 @@ __device__ __forceinline__ void combine_unit(const CombineArgs& a, int64_t t, in
     w[k] = k < a.K ? __ldg(a.weights + (size_t)t * a.K + k) : 0.0f;
   }
 #pragma unroll
-  for (int k = 0; k < KT; ++k)
-    if (pos[k] >= 0) yv[k] = __ldcs(row_of<EP>(a, t, k, pos[k]) + v);
+  for (int k = 0; k < KT; ++k) {
+    if (pos[k] >= 0) {
+      const uint4* src = row_of<EP>(a, t, k, pos[k]);
+      if (EP && src == nullptr)
+        pos[k] = -1;  // no row on the owner: the pair contributes nothing
+      else
+        yv[k] = __ldcs(src + v);
+    }
+  }
   float acc[8];
   if (a.shared != nullptr) {
     const uint4 s = __ldcs(a.shared + (size_t)t * a.nvec + v);
@@ -115,8 +126,15 @@ __device__ __forceinline__ void combine_unit_any(const CombineArgs& a, int64_t t
       w[k] = k0 + k < a.K ? __ldg(a.weights + (size_t)t * a.K + k0 + k) : 0.0f;
     }
 #pragma unroll
-    for (int k = 0; k < 8; ++k)
-      if (pos[k] >= 0) yv[k] = __ldcs(row_of<EP>(a, t, k0 + k, pos[k]) + v);
+    for (int k = 0; k < 8; ++k) {
+      if (pos[k] >= 0) {
+        const uint4* src = row_of<EP>(a, t, k0 + k, pos[k]);
+        if (EP && src == nullptr)
+          pos[k] = -1;
+        else
+          yv[k] = __ldcs(src + v);
+      }
+    }
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
       if (pos[k] >= 0) {

@@ -74,8 +74,6 @@ cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b,
 cudaError_t launch_gemv_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                               float* logits_out, int32_t* ids, int32_t* tile_base, int32_t* counts, int32_t* ticket,
                               cudaStream_t s);
-cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                        int32_t* tile_base, int32_t* counts, cudaStream_t s);
 cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
                            const int32_t* ids, const int32_t* tile_base, const int32_t* counts,
                            int32_t* status, int32_t* dense, const int32_t* group_counts, cudaStream_t s,
@@ -83,6 +81,7 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
 bool umma_available();
 bool gemv_eligible(const moe_rd_params& p);
 void count_launch(int n = 1);
+void set_last_cuda_error(cudaError_t e);  // what moe_rd_last_cuda_error reports on this thread
 
 // ---------------------------------------------------------------------------
 // device helpers

@@ -192,9 +192,14 @@ __device__ __forceinline__ void epilogue_rows(const UmmaArgs& a, unsigned char* 
     if (a.zero != nullptr) {
       // Clear the counters of the later kernels while the first tiles are on
       // their way (the routing kernel starts after this grid has finished).
+      // The region starts with the status block (16 vectors).  Only the first CTA clears
+      // that, at its very start: a CTA of a later wave must not wipe a time-out another
+      // CTA has recorded there (a report is at least 2^20 polls after the kernel began).
       const uint32_t nthr = gridDim.x * gridDim.y * 128u;
-      const uint32_t me = (blockIdx.y * gridDim.x + blockIdx.x) * 128u + (uint32_t)(q * 32 + lane);
-      for (uint32_t i = me; i < a.zero_vecs; i += nthr) a.zero[i] = make_uint4(0u, 0u, 0u, 0u);
+      const uint32_t cta = blockIdx.y * gridDim.x + blockIdx.x;
+      const uint32_t me = cta * 128u + (uint32_t)(q * 32 + lane);
+      for (uint32_t i = me; i < a.zero_vecs; i += nthr)
+        if (i >= 16u || cta == 0u) a.zero[i] = make_uint4(0u, 0u, 0u, 0u);
     }
     bool ok = mbar_wait(smem_u32(accum_bar), 0u, abort_flag);
     ok = __all_sync(kFull, ok);

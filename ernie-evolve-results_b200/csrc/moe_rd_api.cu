@@ -14,6 +14,7 @@ static std::atomic<int64_t> g_launches{0};
 static thread_local cudaError_t t_last_cuda = cudaSuccess;
 
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+void set_last_cuda_error(cudaError_t e) { t_last_cuda = e; }
 
 cudaError_t init_route_attributes();
 cudaError_t init_umma_attributes();
@@ -274,9 +275,11 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[2], s));
   // the fused GEMV kernel scans in its last block; after the routing kernel the positions kernel
-  // derives bases and offsets itself; with T = 0 nothing ran and the scan kernel writes the zeros
-  if (p->T == 0)
-    MOE_RD_CUDA(launch_scan(*p, *b, plan, tile_base, counts, s));
+  // derives bases and offsets itself; with T = 0 nothing ran: every offset and count is zero
+  if (p->T == 0) {
+    MOE_RD_CUDA(cudaMemsetAsync(b->offsets, 0, (size_t)(p->E + 1) * 4, s));
+    if (b->counts != nullptr) MOE_RD_CUDA(cudaMemsetAsync(b->counts, 0, (size_t)p->E * 4, s));
+  }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[3], s));
   MOE_RD_CUDA(launch_scatter(*p, *b, plan, ids, tile_base, counts, status,
                              reinterpret_cast<int32_t*>(ws + w.dense), group_counts, s, ev ? ev[4] : nullptr));

@@ -20,16 +20,38 @@ void* g_scratch_ptr[64] = {};  // device address of g_noalloc_scratch, per devic
 // once per device, with that device current.
 int scratch_for_current_device(void** out) {
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return MOE_RD_E_CUDA;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    moe_rd::set_last_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidDevice);
+    return MOE_RD_E_CUDA;
+  }
   std::lock_guard<std::mutex> lock(g_mu);
   if (g_scratch_ptr[dev] == nullptr) {
     void* p = nullptr;
-    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr)
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      moe_rd::set_last_cuda_error(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
       return MOE_RD_E_CUDA;
+    }
     g_scratch_ptr[dev] = p;
   }
   *out = g_scratch_ptr[dev];
   return MOE_RD_OK;
+}
+
+// The kernels run on the device of the stream; the scratch address belongs to the
+// current device.  Refuse a stream of another device instead of handing its
+// kernels an address of this one.
+int stream_is_on_current_device(void* stream) {
+  if (stream == nullptr) return MOE_RD_OK;  // the default stream of the current device
+  int cur = 0, sdev = 0;
+  cudaError_t e = cudaGetDevice(&cur);
+  if (e == cudaSuccess) e = cudaStreamGetDevice(static_cast<cudaStream_t>(stream), &sdev);
+  if (e != cudaSuccess) {
+    moe_rd::set_last_cuda_error(e);
+    return MOE_RD_E_CUDA;
+  }
+  return sdev == cur ? MOE_RD_OK : MOE_RD_E_UNSUPPORTED;
 }
 
 }  // namespace
@@ -40,6 +62,8 @@ extern "C" int moe_rd_route_dispatch_noalloc(const moe_rd_params* p, const moe_r
   const int rc = moe_rd_workspace_bytes(p, &need);
   if (rc != MOE_RD_OK) return rc;
   if (need > (size_t)MOE_RD_NOALLOC_MAX_BYTES) return MOE_RD_E_TOO_LARGE;
+  const int rd = stream_is_on_current_device(stream);
+  if (rd != MOE_RD_OK) return rd;
   void* scratch = nullptr;
   const int rs = scratch_for_current_device(&scratch);
   if (rs != MOE_RD_OK) return rs;
@@ -47,4 +71,16 @@ extern "C" int moe_rd_route_dispatch_noalloc(const moe_rd_params* p, const moe_r
   // block, tile counts, expert counts) at the head of every call, so what an
   // earlier call left behind does not matter.
   return moe_rd_route_dispatch(p, b, scratch, (size_t)MOE_RD_NOALLOC_MAX_BYTES, stream);
+}
+
+// Device status block of the last moe_rd_route_dispatch_noalloc call on the
+// current device (its scratch address is private to this file, so
+// moe_rd_read_status cannot be pointed at it).
+extern "C" int moe_rd_read_status_noalloc(void* stream, int32_t status[8]) {
+  const int rd = stream_is_on_current_device(stream);
+  if (rd != MOE_RD_OK) return rd;
+  void* scratch = nullptr;
+  const int rs = scratch_for_current_device(&scratch);
+  if (rs != MOE_RD_OK) return rs;
+  return moe_rd_read_status(scratch, stream, status);
 }

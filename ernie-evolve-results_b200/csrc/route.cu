@@ -1,7 +1,8 @@
 // Scoring / top-K / tile histogram for logits that already sit in memory (the
-// tensor-core gate, the order-defining SIMT gate, or caller-supplied logits),
-// and the scan kernel that turns tile counts into tile bases and offsets.
-// The per-token and per-tile device code lives in route_core.cuh.
+// tensor-core gate, the order-defining SIMT gate, or caller-supplied logits).
+// The per-token device code lives in route_core.cuh.  The kernel leaves pair
+// counts per (tile, expert) and per (group of tiles, expert); the positions
+// kernel (scatter.cu) turns them into tile bases and offsets.
 #include "route_core.cuh"
 
 namespace moe_rd {
@@ -104,81 +105,6 @@ __global__ void __launch_bounds__(kRouteThreads, MB) route_kernel(const RouteArg
   flush_counts(a, s_cnt, kRouteThreads, group);
 }
 
-// ---------------------------------------------------------------------------
-// One block per expert: exclusive scan of that expert's per-tile counts (in
-// place, -> tile bases) and the expert's first row, offsets[e] = sum over the
-// experts before it of min(count, capacity).  The routing kernels already
-// accumulated counts[E], so no block waits for another.  Replaces the scan part
-// of offsets_kernel (kernel.cu:2074-2086); offsets is stored as E+1 exclusive
-// starts instead of the reference's inclusive ends `offs` plus exclusive starts
-// `cursor`.
-// ---------------------------------------------------------------------------
-constexpr int kScanThreads = 256;
-
-// Exclusive scan of v across the block; returns the exclusive prefix and the
-// block total.  s_w holds one int per warp.
-__device__ __forceinline__ int block_exclusive_scan(int v, int* s_w, int& total) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  int incl = v;
-#pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int n = __shfl_up_sync(kFull, incl, o);
-    if (lane >= o) incl += n;
-  }
-  if (lane == 31) s_w[warp] = incl;
-  __syncthreads();
-  int wp = 0, tot = 0;
-#pragma unroll
-  for (int w = 0; w < kScanThreads / 32; ++w) {
-    const int sv = s_w[w];
-    if (w < warp) wp += sv;
-    tot += sv;
-  }
-  __syncthreads();  // s_w may be reused by the next call
-  total = tot;
-  return wp + incl - v;
-}
-
-__global__ void __launch_bounds__(kScanThreads)
-scan_kernel(int32_t* __restrict__ tile_base, const int32_t* __restrict__ counts,
-            int32_t* __restrict__ user_counts, int32_t* __restrict__ offsets, int E, int ntiles,
-            int64_t capacity) {
-  __shared__ int s_w[kScanThreads / 32];
-  // Wait first, then let the next kernel start: the positions kernel reads the
-  // routing kernel's ids before its own wait, which is safe only once this grid
-  // has seen the routing kernel complete.
-  pdl_wait();
-  pdl_trigger();
-  const int e = blockIdx.x, tid = threadIdx.x;
-  // rows kept by the experts before this one (and by this one, for offsets[E])
-  int before = 0, mine = 0;
-  for (int i = tid; i <= e; i += kScanThreads) {
-    int v = counts[i];
-    if (i == e) {
-      if (user_counts != nullptr) user_counts[e] = v;
-    }
-    if (capacity > 0 && (int64_t)v > capacity) v = (int)capacity;
-    if (i < e) before += v; else mine = v;
-  }
-  int32_t* col = tile_base + (size_t)e * ntiles;
-  int carry = 0;
-  for (int base = 0; base < ntiles; base += kScanThreads) {
-    const int i = base + tid;
-    const int v = i < ntiles ? col[i] : 0;
-    int total;
-    const int ex = block_exclusive_scan(v, s_w, total);
-    if (i < ntiles) col[i] = carry + ex;
-    carry += total;
-  }
-  int total_before, total_mine;
-  block_exclusive_scan(before, s_w, total_before);
-  block_exclusive_scan(mine, s_w, total_mine);
-  if (tid == 0) {
-    offsets[e] = total_before;
-    if (e == E - 1) offsets[E] = total_before + total_mine;
-  }
-}
-
 }  // namespace
 
 int device_sms() {
@@ -275,15 +201,6 @@ cudaError_t launch_route_splits(const moe_rd_params& p, const moe_rd_buffers& b,
     MOE_RD_ROUTE_CASE(8)
   }
 #undef MOE_RD_ROUTE_CASE
-  count_launch();
-  return e;
-}
-
-cudaError_t launch_scan(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,
-                        int32_t* tile_base, int32_t* counts, cudaStream_t s) {
-  const cudaError_t e = launch_pdl(scan_kernel, dim3((unsigned)p.E), dim3(kScanThreads), 0, s,
-                                   tile_base, (const int32_t*)counts, b.counts, b.offsets, p.E,
-                                   plan.ntiles, p.capacity);
   count_launch();
   return e;
 }

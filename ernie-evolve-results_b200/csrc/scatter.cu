@@ -47,9 +47,6 @@ namespace {
 #ifndef MOE_RD_SC_VECTOR_SCALES   // 1: the four scales of an fp8 work unit leave in one 16-byte store
 #define MOE_RD_SC_VECTOR_SCALES 0
 #endif
-#ifndef MOE_RD_POS_EARLY_IDS   // 1: the positions kernel ranks pairs while the scan kernel still runs
-#define MOE_RD_POS_EARLY_IDS 1
-#endif
 #ifndef MOE_RD_SC_STREAMING   // 1: st.global.cs (evict-first) for the row stores
 #define MOE_RD_SC_STREAMING 1
 #endif
@@ -81,7 +78,6 @@ struct PositionArgs {
   int32_t* dense;            // [1+kMaxK] identity experts: number, first rows (or null)
   int64_t T, capacity, out_rows;
   int E, K, ntiles;
-  int early_ids;             // 1: a scan kernel precedes this one (see positions_kernel)
 };
 
 constexpr int kPosThreads = 256;
@@ -92,7 +88,9 @@ static_assert(kMaxE <= kPosThreads, "tile mode keeps one expert per thread");
 // same expert: every 32 consecutive pairs are counted with __match_any_sync and
 // the per-chunk counts are prefix-summed per expert in pair order.
 //
-// TILE (after the routing kernel of route.cu): there is no scan kernel; the block
+// Scanned mode (after the fused GEMV kernel, whose last block scanned the counts):
+// tile_base [E][ntiles] and offsets are read as they are.
+// TILE (after the routing kernel of route.cu): there is no scan; the block
 // derives what it needs from the raw counts itself, thread e for expert e, with
 // coalesced loads that are all in flight at once: the expert's total (sum of its
 // group counts), the pairs in the tiles before this one (group counts of the
@@ -119,13 +117,8 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
     const int nw = (nch * a.E + 1) >> 1;
     for (int i = tid; i < nw; i += kPosThreads) z32[i] = 0u;
   }
-  // The ids come from the routing kernel, the tile bases and offsets from the
-  // scan kernel after it.  When a scan kernel precedes this one (early_ids), it
-  // lets this grid start only after it has itself seen the routing kernel
-  // complete, so the ids may be read - and the in-tile ranks computed - while the
-  // scan kernel is still running; only the last pass waits for it.
   pdl_trigger();
-  if (TILE || !a.early_ids) pdl_wait();
+  pdl_wait();
   int e_reg[kRegChunks], tb_reg[kRegChunks], off_reg[kRegChunks];
 #pragma unroll
   for (int k = 0; k < kRegChunks; ++k) {
@@ -134,8 +127,8 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
     e_reg[k] = e;
     tb_reg[k] = 0;
     off_reg[k] = 0;
-    if (!TILE && !a.early_ids && e >= 0 && e < a.E) {
-      // no scan kernel to overlap with: every load is issued up front
+    if (!TILE && e >= 0 && e < a.E) {
+      // scanned mode: every load is issued up front
       tb_reg[k] = a.tile_base[(size_t)e * a.ntiles + tile];
       off_reg[k] = a.offsets[e];
     }
@@ -217,17 +210,6 @@ __global__ void __launch_bounds__(kPosThreads) positions_kernel(const PositionAr
       const int v = s_cc[c * a.E + e];
       s_cc[c * a.E + e] = (uint16_t)run;
       run += v;
-    }
-  }
-  if (!TILE && a.early_ids) {
-    pdl_wait();
-#pragma unroll
-    for (int k = 0; k < kRegChunks; ++k) {
-      const int e = e_reg[k];
-      if (e >= 0 && e < a.E) {
-        tb_reg[k] = a.tile_base[(size_t)e * a.ntiles + tile];
-        off_reg[k] = a.offsets[e];
-      }
     }
   }
   __syncthreads();
@@ -334,10 +316,12 @@ __device__ __forceinline__ bool resolve_dest(const ScatterArgs& a, int64_t t, in
     return true;
   }
   const int e = __ldg(a.ids + (size_t)t * a.K + k);
+  const int db = __ldg(a.dest_base + e);
+  if (db < 0) return false;  // the expert's rows do not fit its owner's buffer (moe_rd_ep_plan reported it)
   const int d = e / a.epr;
   rows = a.peer_rows[d];
   scales = a.peer_scales[d];
-  row = (int64_t)__ldg(a.dest_base + e) + (q - __ldg(a.offsets + e));
+  row = (int64_t)db + (q - __ldg(a.offsets + e));
   return true;
 }
 
@@ -581,20 +565,6 @@ __global__ void __launch_bounds__(kScatterThreads) scatter_kernel(const ScatterA
   }
 }
 
-// Every rank writes its kept rows per expert into slot `rank` of every peer's
-// [world][E] table (peer stores of E ints each): the count exchange without a
-// library collective; a cross-rank barrier follows on the stream.
-struct PushArgs {
-  int32_t* peer_kept[kMaxWorld];
-};
-__global__ void ep_push_counts_kernel(const int32_t* __restrict__ offsets, int E, int rank, int world,
-                                      const PushArgs pa) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
-  if (e >= E) return;
-  const int kept = offsets[e + 1] - offsets[e];
-  for (int d = 0; d < world; ++d) pa.peer_kept[d][(size_t)rank * E + e] = kept;
-}
-
 }  // namespace
 
 int device_sms();
@@ -643,7 +613,6 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
   pa.E = p.E;
   pa.K = p.K;
   pa.ntiles = plan.ntiles;
-  pa.early_ids = (plan.gate != MOE_RD_GATE_GEMV && !plan.tile_major && MOE_RD_POS_EARLY_IDS) ? 1 : 0;
   cudaError_t e = plan.tile_major ? launch_pdl(positions_kernel<true>, dim3((unsigned)plan.ntiles),
                                                dim3(kPosThreads), positions_smem(p.K, p.E), s, pa)
                                   : launch_pdl(positions_kernel<false>, dim3((unsigned)plan.ntiles),
@@ -702,22 +671,28 @@ ep_plan_kernel(const int32_t* __restrict__ kept_all, int world, int rank, int E,
     s_before[e] = before;
   }
   __syncthreads();
-  // exclusive prefix of s_tot inside every owner's expert range (<= 256 entries)
+  // exclusive prefix of s_tot inside every owner's expert range (<= 256 entries).
+  // Every rank computes the same table from the same counts, so every rank sees
+  // the same overflow: an expert whose rows would end past max_rows in its
+  // owner's buffer gets no destination (-1) on any rank, and its pairs are
+  // skipped by the scatter and combine kernels instead of being stored or loaded
+  // out of bounds.
   if (threadIdx.x < world) {
     const int d = threadIdx.x;
-    int run = 0;
+    int64_t run = 0;
+    bool over = false;
     for (int le = 0; le < epr; ++le) {
-      s_start[d * epr + le] = run;
-      if (d == rank) local_offsets[le] = run;
+      over = over || run + s_tot[d * epr + le] > max_rows;
+      s_start[d * epr + le] = over ? -1 : (int)run;
+      if (d == rank) local_offsets[le] = (int)(run < max_rows ? run : max_rows);
       run += s_tot[d * epr + le];
     }
-    if (d == rank) {
-      local_offsets[epr] = run;
-      if ((int64_t)run > max_rows) report(status, 202, run, (int)max_rows);
-    }
+    if (d == rank) local_offsets[epr] = (int)(run < max_rows ? run : max_rows);
+    if (over) report(status, 202, (int)(run > 0x7fffffff ? 0x7fffffff : run), d);
   }
   __syncthreads();
-  for (int e = threadIdx.x; e < E; e += blockDim.x) dest_base[e] = s_start[e] + s_before[e];
+  for (int e = threadIdx.x; e < E; e += blockDim.x)
+    dest_base[e] = s_start[e] < 0 ? -1 : s_start[e] + s_before[e];
   for (int i = threadIdx.x; i < world * epr; i += blockDim.x) {
     const int s = i / epr, le = i - s * epr;
     cnt[i] = max(kept_all[(size_t)s * E + rank * epr + le], 0);
@@ -744,22 +719,6 @@ extern "C" int moe_rd_ep_plan(const int32_t* kept_all, int world, int rank, int 
   return cudaGetLastError() == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
 }
 
-extern "C" int moe_rd_ep_push_counts(const int32_t* offsets, int E, int rank, int world,
-                                     int32_t* const* peer_kept, void* stream) {
-  if (offsets == nullptr || peer_kept == nullptr) return MOE_RD_E_NULL;
-  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || E < 1 || E > kMaxE)
-    return MOE_RD_E_SHAPE;
-  PushArgs pa = {};
-  for (int d = 0; d < world; ++d) {
-    if (peer_kept[d] == nullptr) return MOE_RD_E_NULL;
-    pa.peer_kept[d] = peer_kept[d];
-  }
-  ep_push_counts_kernel<<<(E + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(offsets, E, rank,
-                                                                                         world, pa);
-  count_launch();
-  return cudaGetLastError() == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
-}
-
 extern "C" int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const int32_t* expert_ids,
                                  const int32_t* inverse_perm, const int32_t* offsets,
                                  const int32_t* dest_base, int world, void* const* peer_rows,
@@ -770,14 +729,17 @@ extern "C" int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const in
   if (world < 1 || world > kMaxWorld || p->E % world != 0 || p->T < 0 || p->H % 8 != 0)
     return MOE_RD_E_SHAPE;
   const bool fp8 = p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128;
-  if (fp8 && (peer_scales == nullptr || p->H % 128 != 0)) return MOE_RD_E_NULL;
+  if (fp8 && p->H % 128 != 0) return MOE_RD_E_SHAPE;
+  // fp8 rows without a scales buffer: the scales follow each row (bulk copies only)
+  const bool packed = fp8 && peer_scales == nullptr;
+  if (packed && p->scatter_impl != MOE_RD_SCATTER_BULK) return MOE_RD_E_NULL;
   if (p->T == 0) return MOE_RD_OK;
   if (p->scatter_impl == MOE_RD_SCATTER_BULK) {
     // whole-row bulk copies (TMA engine) into the owners' buffers
     if (!bulk_scatter_eligible(*p)) return MOE_RD_E_UNSUPPORTED;
     for (int d = 0; d < world; ++d)
-      if ((reinterpret_cast<uintptr_t>(peer_rows[d]) & 15) ||
-          (fp8 && (reinterpret_cast<uintptr_t>(peer_scales[d]) & 15)))
+      if (peer_rows[d] == nullptr || (reinterpret_cast<uintptr_t>(peer_rows[d]) & 15) ||
+          (fp8 && !packed && (peer_scales[d] == nullptr || (reinterpret_cast<uintptr_t>(peer_scales[d]) & 15))))
         return MOE_RD_E_ALIGN;
     if (status == nullptr) return MOE_RD_E_NULL;
     const cudaError_t be =

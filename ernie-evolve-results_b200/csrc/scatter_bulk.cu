@@ -89,24 +89,29 @@ struct BulkArgs {
   void* peer_rows[kMaxWorld];
   float* peer_scales[kMaxWorld];
   int epr;
+  int packed;  // 1 (expert-parallel fp8): a destination row is H bytes followed by its H/128 scales
 };
 
-// Destination of pair (t,k) with local row q >= 0: buffers and row to write.
+// Destination of pair (t,k) with local row q >= 0: buffers and row to write;
+// false when the pair has none (its expert's rows do not fit the owner's buffer).
 template <bool EP>
-__device__ __forceinline__ void bulk_dest(const BulkArgs& a, int64_t t, int k, int q,
+__device__ __forceinline__ bool bulk_dest(const BulkArgs& a, int64_t t, int k, int q,
                                           unsigned char*& rows, unsigned char*& scales,
                                           int64_t& row) {
   if (!EP) {
     rows = static_cast<unsigned char*>(a.rows);
     scales = reinterpret_cast<unsigned char*>(a.scales);
     row = q;
-    return;
+    return true;
   }
   const int e = __ldg(a.ids + (size_t)t * a.K + k);
+  const int db = __ldg(a.dest_base + e);
+  if (db < 0) return false;
   const int d = e / a.epr;
   rows = static_cast<unsigned char*>(a.peer_rows[d]);
   scales = reinterpret_cast<unsigned char*>(a.peer_scales[d]);
-  row = (int64_t)__ldg(a.dest_base + e) + (q - __ldg(a.offsets + e));
+  row = (int64_t)db + (q - __ldg(a.offsets + e));
+  return true;
 }
 
 // ------------------------------ bf16 --------------------------------------
@@ -151,8 +156,7 @@ __global__ void __launch_bounds__(32) scatter_bulk_bf16_kernel(const BulkArgs a)
     if (pos >= 0) {
       unsigned char *out, *unused;
       int64_t r;
-      bulk_dest<EP>(a, t, lane, pos, out, unused, r);
-      bulk_store(out + (size_t)r * row_bytes, src, row_bytes);
+      if (bulk_dest<EP>(a, t, lane, pos, out, unused, r)) bulk_store(out + (size_t)r * row_bytes, src, row_bytes);
     }
     bulk_commit();
     // the stage may be refilled once every lane's stores have read it
@@ -244,9 +248,15 @@ __global__ void __launch_bounds__(kQThreads) scatter_bulk_fp8_kernel(const BulkA
       if (pos >= 0) {
         unsigned char *out_q, *out_s;
         int64_t r;
-        bulk_dest<EP>(a, t, tid, pos, out_q, out_s, r);
-        bulk_store(out_q + (size_t)r * q_bytes, smem_u32(buf), q_bytes);
-        bulk_store(out_s + (size_t)r * s_bytes, smem_u32(buf + q_bytes), s_bytes);
+        if (bulk_dest<EP>(a, t, tid, pos, out_q, out_s, r)) {
+          if (a.packed) {
+            // scales follow their row in the destination: the shared image goes out in one copy
+            bulk_store(out_q + (size_t)r * (q_bytes + s_bytes), smem_u32(buf), q_bytes + s_bytes);
+          } else {
+            bulk_store(out_q + (size_t)r * q_bytes, smem_u32(buf), q_bytes);
+            bulk_store(out_s + (size_t)r * s_bytes, smem_u32(buf + q_bytes), s_bytes);
+          }
+        }
       }
       bulk_commit();
     }
@@ -343,6 +353,7 @@ cudaError_t launch_scatter_bulk_ep(const moe_rd_params& p, const void* x, const 
     a.peer_rows[d] = peer_rows[d];
     a.peer_scales[d] = peer_scales != nullptr ? peer_scales[d] : nullptr;
   }
+  a.packed = (peer_scales == nullptr && p.rows_format == MOE_RD_ROWS_FP8_E4M3_B128) ? 1 : 0;
   return launch_bulk_args(p, a, true, s);
 }
 

@@ -114,29 +114,34 @@ class ExpertParallel:
 class ExpertParallelFused:
     """Expert-parallel dispatch without a send buffer: after the counts are
     gathered, ONE kernel reads each token row once and stores it straight into
-    the owner's expert-major buffer over NVLink (plain 16-byte peer stores, no
-    multicast), already at its final row, so there is no receive-side reorder.
+    the owner's expert-major buffer over NVLink (peer stores, no multicast),
+    already at its final row, so there is no receive-side reorder.
     Use a ``Session(..., scatter_impl="none")``.
 
     The receive buffers live in symmetric memory (torch's intra-node peer
-    mapping) and are sized once for the worst case.  ``exchange`` synchronises
-    nothing on the host: gather of counts (NCCL), plan kernel, scatter kernel,
-    and a one-element all-reduce that orders every rank's stores before anyone
-    reads its buffer.  With ``sync="symm"`` the counts are pushed
-    into the peers' tables by a small kernel and the two synchronisations are
-    symmetric-memory signal barriers instead of NCCL collectives.
+    mapping) and are sized once, ``max_recv_rows`` rows on every rank (default:
+    the worst case, every rank sending all its rows here).  ``exchange``
+    synchronises nothing on the host: all-gather of the counts (NCCL; it is also
+    the barrier that protects the previous step's buffers), plan kernel, scatter
+    kernel, and a one-element all-reduce that orders every rank's stores before
+    anyone reads its buffer.  NCCL's collectives end with an error, through the
+    process group's timeout, when a rank never arrives; no kernel here waits on
+    another rank.
+
+    ``layout``: "packed" (fp8 rows moved by bulk copies, the default there): a
+    received row is H bytes followed by its H/128 scales, so a pair crosses
+    NVLink as one copy; ``rows`` and ``scales`` are strided views of that
+    buffer.  "separate": rows and scales in two dense buffers (two copies per
+    pair).  Both hold the same values.
+
+    If the rows bound for some rank exceed ``max_recv_rows``, the plan kernel
+    records it (``check()`` raises) and the experts that do not fit receive
+    nothing; no store or load leaves a buffer.
     """
 
     def __init__(self, session, group=None, max_recv_rows: Optional[int] = None,
-                 bulk: Optional[bool] = None, sync: str = "nccl"):
+                 bulk: Optional[bool] = None, layout: Optional[str] = None):
         import torch.distributed._symmetric_memory as symm_mem
-        if sync not in ("symm", "nccl"):
-            raise ValueError("sync must be 'symm' or 'nccl'")
-        # "nccl" (default): all-gather of the counts and one-element all-reduces; "symm": counts are
-        # pushed into the peers' tables by a small kernel and the ranks meet at symmetric-memory signal
-        # barriers.  Both measured the same step time on 2 GPUs (0.483 ms); NCCL's collectives come
-        # with a watchdog for a rank that never arrives, the signal barriers spin until it does.
-        self.sync = sync
         # Whole-row bulk copies (cp.async.bulk through shared memory) measured ~7 % more NVLink
         # bandwidth than 16-byte stores; they need 16-byte aligned scale rows (H % 512 == 0).
         H = session.H
@@ -145,6 +150,13 @@ class ExpertParallelFused:
         if bulk and not ok:
             raise ValueError("bulk expert-parallel scatter is not available for this row size")
         self.bulk = ok if bulk is None else bulk
+        if layout is None:
+            layout = "packed" if (self.bulk and session.fp8) else "separate"
+        if layout not in ("packed", "separate"):
+            raise ValueError("layout must be 'packed' or 'separate'")
+        if layout == "packed" and not (self.bulk and session.fp8):
+            raise ValueError("the packed layout needs fp8 rows moved by bulk copies")
+        self.layout = layout
         self.sess = session
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -159,21 +171,29 @@ class ExpertParallelFused:
         self.nb = H // 128 if self.fp8 else 0
         per_rank = T * K if not session.params.capacity else min(T * K, E * session.params.capacity)
         self.max_rows = int(max_recv_rows if max_recv_rows is not None else self.world * per_rank)
-        rows_bytes = (self.max_rows * self.row_bytes + 255) // 256 * 256
-        total = rows_bytes + self.max_rows * self.nb * 4
-        self.buf = symm_mem.empty(total, dtype=torch.uint8, device=dev)
-        self.hdl = symm_mem.rendezvous(self.buf, self.group)
-        ptrs = [int(p) for p in self.hdl.buffer_ptrs]
-        self.peer_rows = (ctypes.c_void_p * self.world)(*ptrs)
-        self.peer_scales = (ctypes.c_void_p * self.world)(*[p + rows_bytes for p in ptrs])
-        rows_u8 = self.buf[: self.max_rows * self.row_bytes]
-        self.rows = (rows_u8 if self.fp8 else rows_u8.view(torch.bfloat16)).view(self.max_rows, H)
-        self.scales = (self.buf[rows_bytes: rows_bytes + self.max_rows * self.nb * 4].view(torch.float32)
-                       .view(self.max_rows, self.nb)) if self.fp8 else None
-        self.kept_buf = symm_mem.empty(self.world * E, dtype=torch.int32, device=dev)
-        self.kept_hdl = symm_mem.rendezvous(self.kept_buf, self.group)
-        self.peer_kept = (ctypes.c_void_p * self.world)(*[int(p) for p in self.kept_hdl.buffer_ptrs])
-        self.kept_all = self.kept_buf.view(self.world, E)
+        if layout == "packed":
+            pitch = self.row_bytes + self.nb * 4
+            self.buf = symm_mem.empty(self.max_rows * pitch, dtype=torch.uint8, device=dev)
+            self.hdl = symm_mem.rendezvous(self.buf, self.group)
+            ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+            self.peer_rows = (ctypes.c_void_p * self.world)(*ptrs)
+            self.peer_scales = None
+            img2d = self.buf.view(self.max_rows, pitch)
+            self.rows = img2d[:, :H]
+            self.scales = img2d[:, H:].view(torch.float32)
+        else:
+            rows_bytes = (self.max_rows * self.row_bytes + 255) // 256 * 256
+            total = rows_bytes + self.max_rows * self.nb * 4
+            self.buf = symm_mem.empty(total, dtype=torch.uint8, device=dev)
+            self.hdl = symm_mem.rendezvous(self.buf, self.group)
+            ptrs = [int(p) for p in self.hdl.buffer_ptrs]
+            self.peer_rows = (ctypes.c_void_p * self.world)(*ptrs)
+            self.peer_scales = (ctypes.c_void_p * self.world)(*[p + rows_bytes for p in ptrs])
+            rows_u8 = self.buf[: self.max_rows * self.row_bytes]
+            self.rows = (rows_u8 if self.fp8 else rows_u8.view(torch.bfloat16)).view(self.max_rows, H)
+            self.scales = (self.buf[rows_bytes: rows_bytes + self.max_rows * self.nb * 4].view(torch.float32)
+                           .view(self.max_rows, self.nb)) if self.fp8 else None
+        self.kept_all = torch.empty((self.world, E), dtype=torch.int32, device=dev)
         self.dest_base = torch.empty(E, dtype=torch.int32, device=dev)
         self.cnt = torch.empty((self.world, self.epr), dtype=torch.int32, device=dev)
         self.local_offsets = torch.empty(self.epr + 1, dtype=torch.int32, device=dev)
@@ -190,12 +210,8 @@ class ExpertParallelFused:
             return ctypes.c_void_p(t.data_ptr())
         L = _cabi.lib()
         # the count exchange is also a barrier: nobody overwrites a buffer its owner may still be reading
-        if self.sync == "nccl":
-            kept = (offs[1:] - offs[:-1]).contiguous()
-            dist.all_gather_into_tensor(self.kept_all, kept, group=self.group)
-        else:
-            _cabi.check(L.moe_rd_ep_push_counts(ptr(offs), self.sess.E, self.rank, self.world, self.peer_kept, stream))
-            self.kept_hdl.barrier(channel=0)
+        kept = (offs[1:] - offs[:-1]).contiguous()
+        dist.all_gather_into_tensor(self.kept_all, kept, group=self.group)
         _cabi.check(L.moe_rd_ep_plan(ptr(self.kept_all), self.world, self.rank, self.sess.E, self.max_rows,
                                      ptr(self.dest_base), ptr(self.cnt), ptr(self.local_offsets), ptr(self.status),
                                      stream))
@@ -206,14 +222,20 @@ class ExpertParallelFused:
         _cabi.check(L.moe_rd_ep_scatter(ctypes.byref(params), ptr(x), ptr(r.expert_ids),
                                         ptr(r.inverse_perm), ptr(offs), ptr(self.dest_base), self.world,
                                         self.peer_rows, self.peer_scales, ptr(self.status), stream))
-        self._barrier(1)  # every rank's stores are done and visible after this
+        self._barrier()  # every rank's stores are done and visible after this
         return EPResult(self.rows, self.scales, self.local_offsets, self.cnt, -1, -1)
 
-    def _barrier(self, channel: int) -> None:
-        if self.sync == "nccl":
-            dist.all_reduce(self.token, group=self.group)
-        else:
-            self.hdl.barrier(channel=channel)
+    def _barrier(self) -> None:
+        dist.all_reduce(self.token, group=self.group)
+
+    def check(self) -> None:
+        """Reads the device status block of this object's kernels (synchronises)
+        and raises if one of them recorded a failed check, e.g. id 202: the rows
+        bound for a rank exceed ``max_recv_rows``."""
+        st = [int(v) for v in self.status.cpu()]
+        if st[0] != 0:
+            self.status.zero_()
+            raise _cabi.MoeRdError(-9, f"device status {st}")
 
     def expert_output_buffer(self) -> torch.Tensor:
         """[max_recv_rows, H] bf16 in symmetric memory: the experts of this rank
@@ -239,7 +261,7 @@ class ExpertParallelFused:
         T, K, H, E = self.sess.T, self.sess.K, self.sess.H, self.sess.E
         dev = self.buf.device
         out = torch.empty((T, H), dtype=torch.bfloat16, device=dev)
-        self._barrier(2)
+        self._barrier()
         stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
         def ptr(t):
@@ -248,5 +270,5 @@ class ExpertParallelFused:
         _cabi.check(_cabi.lib().moe_rd_ep_combine(
             T, H, K, E, self.world, self.peer_y, ptr(r.expert_ids), ptr(r.inverse_perm), ptr(r.combine_weights),
             ptr(r.offsets), ptr(self.dest_base), ptr(sh), ptr(out), stream))
-        self._barrier(3)
+        self._barrier()
         return out

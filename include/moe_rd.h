@@ -152,7 +152,15 @@ int moe_rd_route_dispatch(const moe_rd_params* p, const moe_rd_buffers* b,
  * The caller still passes all inputs and outputs in `b`.
  *
  * - Problems whose moe_rd_workspace_bytes() exceeds MOE_RD_NOALLOC_MAX_BYTES are
- *   refused with MOE_RD_E_TOO_LARGE before anything is launched.
+ *   refused with MOE_RD_E_TOO_LARGE before anything is launched.  That size is the
+ *   worst case (it includes room for the logits and expert ids even when the
+ *   caller passes router_logits / expert_ids buffers of its own), so a problem
+ *   can be refused although this particular call would have needed less.
+ * - `stream` must belong to the current device (MOE_RD_E_UNSUPPORTED otherwise):
+ *   the scratch address is looked up for the current device.
+ * - moe_rd_read_status_noalloc reads the device status block of the last such
+ *   call on the current device (synchronises `stream`), as moe_rd_read_status
+ *   does for a caller-owned workspace.
  * - The call itself makes no cudaMalloc/cudaFree and uses no allocating library.
  * - The first call on each device looks up the array's device address (and, as
  *   with moe_rd_route_dispatch, sets kernel attributes); make that first call
@@ -166,6 +174,7 @@ int moe_rd_route_dispatch(const moe_rd_params* p, const moe_rd_buffers* b,
  */
 #define MOE_RD_NOALLOC_MAX_BYTES (32u << 20)
 int moe_rd_route_dispatch_noalloc(const moe_rd_params* p, const moe_rd_buffers* b, void* stream);
+int moe_rd_read_status_noalloc(void* stream, int32_t status[8]);
 
 /*
  * Expert-parallel receive side.  After an all-to-all delivered, from every
@@ -193,8 +202,11 @@ int moe_rd_ep_unpack(const int32_t* cnt, int world, int experts_per_rank, const 
  * the owner's buffer where THIS rank's rows for expert e start (experts of an
  * owner are contiguous, and inside an expert rows are ordered by source rank),
  * cnt[world][E/world] = rows this rank receives per (source, local expert), and
- * local_offsets[E/world + 1].  status word 0 is set if this rank would receive
- * more than max_rows.
+ * local_offsets[E/world + 1].  max_rows is the number of rows of EVERY rank's
+ * buffer.  If the rows of an expert would end past max_rows in its owner's
+ * buffer, status word 0 is set (id 202) on every rank, that expert gets
+ * dest_base = -1 everywhere, and moe_rd_ep_scatter / moe_rd_ep_combine skip its
+ * pairs: nothing is stored or loaded outside a buffer.
  *
  * moe_rd_ep_scatter: for every kept pair (t,k) of this rank, row
  * dest_base[e] + (inverse_perm[t,k] - offsets[e]) of the owner's buffer
@@ -204,7 +216,10 @@ int moe_rd_ep_unpack(const int32_t* cnt, int world, int experts_per_rank, const 
  * entry for `rank` is local).  Plain 16-byte stores; no multicast.  The caller
  * orders a cross-rank barrier after it before anyone reads the buffers.
  * p->scatter_impl = MOE_RD_SCATTER_BULK moves whole rows with cp.async.bulk
- * through shared memory instead (needs `status`, an 8-word device block).
+ * through shared memory instead (needs `status`, an 8-word device block).  With
+ * bulk copies and fp8 rows peer_scales may be NULL: a row of peer_rows[d] is then
+ * H bytes followed by its H/128 fp32 scales (pitch H + H/32 bytes), and a pair
+ * crosses NVLink as ONE copy instead of two.
  * Run the local pipeline with MOE_RD_SCATTER_NONE first.  No counterpart in the
  * reference (it has no expert parallelism).
  */
@@ -233,7 +248,8 @@ int moe_rd_combine(int64_t T, int32_t H, int32_t K, const void* y, const int32_t
  * `stream` between the stages; synchronises the stream and returns the device
  * time of each stage in milliseconds: stage_ms[0] gate product, [1] scoring /
  * top-k / expert histogram (with the fused GEMV gate the product and the scans
- * are in here), [2] scans, [3] positions, [4] row scatter.  For measurement only
+ * are in here), [2] unused (no separate scan kernel is launched), [3] positions
+ * (tile bases, offsets, inverse permutation), [4] row scatter.  For measurement only
  * (the reference's per-kernel figures come from an external profiler,
  * kernel.cu:865-890); it creates and destroys events, so keep it off hot paths.
  */
@@ -250,16 +266,6 @@ int moe_rd_route_dispatch_timed(const moe_rd_params* p, const moe_rd_buffers* b,
  * on external compute-sanitizer runs (kernel.cu:4193-4195).
  */
 int moe_rd_read_status(const void* workspace, void* stream, int32_t status[8]);
-
-/*
- * Count exchange of the expert-parallel dispatch without a library collective:
- * writes kept[e] = offsets[e+1] - offsets[e] of this rank into row `rank` of
- * every peer's [world][E] table (peer_kept[d] = rank d's table, mapped into
- * this process).  The caller follows it with a cross-rank barrier on the stream
- * and then calls moe_rd_ep_plan on its own table.
- */
-int moe_rd_ep_push_counts(const int32_t* offsets, int E, int rank, int world,
-                          int32_t* const* peer_kept, void* stream);
 
 /*
  * Expert-parallel weighted combine: the return path of moe_rd_ep_scatter and the

@@ -72,6 +72,3 @@ def assert_parity(got: dict, ref: dict, *, weight_rtol=1e-6, exact_weights=True)
         np.testing.assert_array_equal(got["combine_weights"].view(np.uint32),
                                       ref["combine_weights"].view(np.uint32), err_msg="combine_weights bits")
 
-
-def read_status(ws_unused=None):
-    return None

@@ -68,7 +68,7 @@ def _setup(name, T, H):
     return dev, p, outputs, buffers, (x, w, bias)
 
 
-def _compare(name, T, H):
+def _compare(name, T, H, warm=True):
     L = _cabi.lib()
     dev, p, outputs, buffers, keep = _setup(name, T, H)
     stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
@@ -80,11 +80,20 @@ def _compare(name, T, H):
     b = buffers(ref)
     _cabi.check(L.moe_rd_route_dispatch(ctypes.byref(p), ctypes.byref(b), ctypes.c_void_p(ws.data_ptr()),
                                         ws_bytes, stream))
-    # workspace-free entry point
+    # workspace-free entry point; the call itself must not take device memory from anyone
     got = outputs()
     b2 = buffers(got)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(dev)
+    held_before = torch.cuda.memory_allocated(dev)
     _cabi.check(L.moe_rd_route_dispatch_noalloc(ctypes.byref(p), ctypes.byref(b2), stream))
     torch.cuda.synchronize()
+    if warm:  # the first call on a device may load the library's device image; later calls change nothing
+        assert torch.cuda.mem_get_info(dev)[0] == free_before
+        assert torch.cuda.memory_allocated(dev) == held_before
+    st = (ctypes.c_int32 * 8)()
+    rc = L.moe_rd_read_status_noalloc(stream, st)
+    assert rc == 0 and st[0] == 0, (rc, list(st))
     R = int(ref["offsets"][-1])
     assert R > 0
     for k in ("offsets", "inverse_perm", "expert_ids", "drop_mask", "counts"):
@@ -98,7 +107,7 @@ def _compare(name, T, H):
 
 
 def test_noalloc_matches_regular_entry_point_on_two_calls_in_a_row():
-    _compare("c4", 700, 1024)   # tensor-core gate, group-limited routing, fp8 rows
+    _compare("c4", 700, 1024, warm=False)   # tensor-core gate, group-limited routing, fp8 rows
     _compare("c3", 3000, 512)   # a different shape on the same scratch: capacity drops, bf16 rows
     _compare("c1", 512, 1024)   # fused GEMV gate
 
