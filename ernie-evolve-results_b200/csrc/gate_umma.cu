@@ -53,8 +53,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
                : "memory");
 }
 // Bounded wait; false when the limit ran out or another role already aborted.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < kSpinLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t limit = kSpinLimit) {
+  for (uint32_t it = 0; it < limit; ++it) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -180,6 +181,8 @@ struct UmmaArgs {
   int mh;          // 128-token halves per CTA (1 or 2): two halves share every W tile
   uint4* zero;     // region the epilogue warps clear while the first tiles load (or null)
   uint32_t zero_vecs;
+  uint32_t spin_limit;  // polls a wait may take before the kernel gives up
+  int no_loads;    // MOE_RD_FLAG_TEST_GATE_STALL: the producer issues nothing, so the waits run out
 };
 
 // Epilogue of one CTA (warps 2..5; TMEM lane = token row of the tile): waits for
@@ -201,7 +204,7 @@ __device__ __forceinline__ void epilogue_rows(const UmmaArgs& a, unsigned char* 
       for (uint32_t i = me; i < a.zero_vecs; i += nthr)
         if (i >= 16u || cta == 0u) a.zero[i] = make_uint4(0u, 0u, 0u, 0u);
     }
-    bool ok = mbar_wait(smem_u32(accum_bar), 0u, abort_flag);
+    bool ok = mbar_wait(smem_u32(accum_bar), 0u, abort_flag, a.spin_limit);
     ok = __all_sync(kFull, ok);
     if (!ok) {
       if (lane == 0 && !*abort_flag) report(a.status, 103, mt, ks);
@@ -311,10 +314,10 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
       int issued = 0;
-      for (int i = 0; i < nkb; ++i) {
+      for (int i = 0; i < nkb && !a.no_loads; ++i) {
         const int s = i % a.stages;
         const uint32_t use = (uint32_t)(i / a.stages);
-        if (!mbar_wait(smem_u32(empty_bar + s), (use & 1u) ^ 1u, abort_flag)) {
+        if (!mbar_wait(smem_u32(empty_bar + s), (use & 1u) ^ 1u, abort_flag, a.spin_limit)) {
           if (!*abort_flag) report(a.status, 101, mt, i);
           *abort_flag = 1;
           break;
@@ -352,7 +355,7 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       for (int i = 0; i < nkb && ok; ++i) {
         const int s = i % a.stages;
         const uint32_t use = (uint32_t)(i / a.stages);
-        if (!mbar_wait(smem_u32(full_bar + s), use & 1u, abort_flag)) {
+        if (!mbar_wait(smem_u32(full_bar + s), use & 1u, abort_flag, a.spin_limit)) {
           if (!*abort_flag) report(a.status, 102, mt, i);
           *abort_flag = 1;
           ok = false;
@@ -457,10 +460,10 @@ gate_umma_pair_kernel(const __grid_constant__ CUtensorMap map_x,
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
       int issued = 0;
-      for (int i = 0; i < nkb; ++i) {
+      for (int i = 0; i < nkb && !a.no_loads; ++i) {
         const int s = i % a.stages;
         const uint32_t use = (uint32_t)(i / a.stages);
-        if (!mbar_wait(smem_u32(empty_bar + s), (use & 1u) ^ 1u, abort_flag)) {
+        if (!mbar_wait(smem_u32(empty_bar + s), (use & 1u) ^ 1u, abort_flag, a.spin_limit)) {
           if (!*abort_flag) report(a.status, 111, mt, i);
           *abort_flag = 1;
           break;
@@ -498,7 +501,7 @@ gate_umma_pair_kernel(const __grid_constant__ CUtensorMap map_x,
       for (int i = 0; i < nkb && ok; ++i) {
         const int s = i % a.stages;
         const uint32_t use = (uint32_t)(i / a.stages);
-        if (!mbar_wait(smem_u32(full_bar + s), use & 1u, abort_flag)) {
+        if (!mbar_wait(smem_u32(full_bar + s), use & 1u, abort_flag, a.spin_limit)) {
           if (!*abort_flag) report(a.status, 112, mt, i);
           *abort_flag = 1;
           ok = false;
@@ -716,6 +719,8 @@ cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, co
   a.w_mn_major = mn_major ? 1 : 0;
   a.zero = static_cast<uint4*>(zero);
   a.zero_vecs = (uint32_t)(zero_bytes / 16);
+  a.no_loads = (p.flags & MOE_RD_FLAG_TEST_GATE_STALL) ? 1 : 0;
+  a.spin_limit = a.no_loads ? 256u : kSpinLimit;
   int cols = 32;
   while (cols < N * a.mh) cols <<= 1;
   a.tmem_cols = cols;

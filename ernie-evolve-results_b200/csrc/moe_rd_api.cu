@@ -114,7 +114,7 @@ static int validate(const moe_rd_params* p) {
   if (p->scatter_impl < MOE_RD_SCATTER_AUTO || p->scatter_impl > MOE_RD_SCATTER_NONE)
     return MOE_RD_E_ENUM;
   if (p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128 && p->H % 128 != 0) return MOE_RD_E_SHAPE;
-  if (p->flags & ~MOE_RD_FLAG_SKIP_IDENTITY_ROWS) return MOE_RD_E_ENUM;
+  if (p->flags & ~(MOE_RD_FLAG_SKIP_IDENTITY_ROWS | MOE_RD_FLAG_TEST_GATE_STALL)) return MOE_RD_E_ENUM;
   if ((p->flags & MOE_RD_FLAG_SKIP_IDENTITY_ROWS) && p->rows_format != MOE_RD_ROWS_BF16)
     return MOE_RD_E_UNSUPPORTED;
   if (p->capacity < 0 || p->out_rows < 0 || p->out_rows > 0x7fffffff) return MOE_RD_E_SHAPE;
@@ -250,7 +250,9 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   // status block, the tile counts and the expert counts are adjacent: one clear.  The
   // tensor-core gate clears them itself (its epilogue warps are idle while the
   // first tiles load), which saves the separate memset node.
-  const bool gate_clears = plan.gate == MOE_RD_GATE_UMMA && p->T > 0;
+  // (not in the time-out test: there a CTA may record its status within microseconds of the start,
+  // before the first CTA has cleared the block)
+  const bool gate_clears = plan.gate == MOE_RD_GATE_UMMA && p->T > 0 && !(p->flags & MOE_RD_FLAG_TEST_GATE_STALL);
   if (!gate_clears) MOE_RD_CUDA(cudaMemsetAsync(ws + w.status, 0, w.zero_bytes, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[0], s));
   if (p->T > 0) {
@@ -259,7 +261,7 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
     } else if (plan.gate == MOE_RD_GATE_UMMA) {
       MOE_RD_CUDA(launch_gate_umma(*p, *b, plan, ws + w.wt,
                                    reinterpret_cast<float*>(ws + w.partial), logits, status,
-                                   ws + w.status, w.zero_bytes, s));
+                                   gate_clears ? ws + w.status : nullptr, w.zero_bytes, s));
     }
   }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[1], s));

@@ -53,6 +53,7 @@ class GemmGroup(ctypes.Structure):
 
 
 FLAG_SKIP_IDENTITY_ROWS = 1
+FLAG_TEST_GATE_STALL = 2
 
 
 class MoeRdError(RuntimeError):

@@ -20,7 +20,7 @@ class Session:
                  n_groups: int = 1, topk_groups: int = 1, group_topk: int = 1, renorm: bool = True,
                  routed_scale: float = 1.0, norm_min: float = 1e-20, capacity: int = 0,
                  rows_format: str = "bf16", gate_impl: str = "auto", scatter_impl: str = "auto",
-                 return_logits: bool = False, top_k: Optional[int] = None):
+                 return_logits: bool = False, top_k: Optional[int] = None, flags: int = 0):
         self.device = torch.device(device)
         if self.device.type != "cuda":
             raise RuntimeError("moe_rd has no CPU path")
@@ -48,7 +48,7 @@ class Session:
             out_rows=out_rows, rows_format=_cabi.ROWS_FORMAT[rows_format],
             w_dtype=_cabi.W_DTYPE["fp32" if w_dtype == torch.float32 else "bf16"],
             w_layout=_cabi.W_LAYOUT[w_layout], gate_impl=_cabi.GATE_IMPL[gate_impl],
-            scatter_impl=_cabi.SCATTER_IMPL[scatter_impl], flags=0)
+            scatter_impl=_cabi.SCATTER_IMPL[scatter_impl], flags=int(flags))
         self.ws_bytes = _cabi.workspace_bytes(self.params)
         self.workspace = torch.empty(self.ws_bytes, dtype=torch.uint8, device=d)
 

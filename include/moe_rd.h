@@ -101,7 +101,18 @@ typedef struct moe_rd_params {
  * groups at x instead.  Same shortcut as ident_a / ident_m of the reference
  * (moe_gemm.h:66-75, kernel.cu:2089-2108, 2154).
  */
-enum { MOE_RD_FLAG_SKIP_IDENTITY_ROWS = 1 };
+enum {
+  MOE_RD_FLAG_SKIP_IDENTITY_ROWS = 1,
+  /* For tests of the time-out path only.  Every wait inside the tensor-core gate
+   * kernel is bounded; when one runs out, the kernel records a status (ids
+   * 101-103, 111, 112), waits for its own copies in flight, frees its tensor
+   * memory and returns, and the call completes with meaningless outputs.  With
+   * this flag the kernel's producer issues no loads at all (so nothing is in
+   * flight) and the limit is a few hundred polls, which makes that path run:
+   * moe_rd_read_status then returns MOE_RD_E_DEVICE and the next call on the same
+   * workspace works normally.  Ignored by the other gate implementations. */
+  MOE_RD_FLAG_TEST_GATE_STALL = 2
+};
 
 /*
  * Device buffers.  The data contract between routing and expert compute that

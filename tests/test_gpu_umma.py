@@ -121,3 +121,41 @@ def test_reference_shape_full_size_default_gate():
 def test_c3_full_size_default_gate():
     t, kw = workloads.make("c3")
     staged_check(t, kw)
+
+
+# ------------------------------------------------------- the time-out path --
+@pytest.mark.parametrize("name,T", [("c4", 1024), ("c3", 512)])
+def test_a_wait_that_runs_out_is_reported_and_the_workspace_stays_usable(name, T):
+    """Every wait inside the tensor-core gate kernel is bounded.  With the test flag the
+    kernel's producer issues no loads (nothing is in flight) and the limit is a few hundred
+    polls, so the waits of the MMA issuer and of the epilogue warps run out: the kernel must
+    record that, free its tensor memory and return; the call completes, the status says so,
+    and the next ordinary call on the same workspace gives the usual bits."""
+    from moe_rd import _cabi
+    from moe_rd.runtime import Session
+    dev = torch.device("cuda:0")
+    t, kw = workloads.make(name, T=T)
+    spec = workloads.SPECS[name]
+    keys = ("score_fn", "bias_mode", "n_groups", "topk_groups", "group_topk", "renorm", "routed_scale", "capacity",
+            "rows_format")
+    skw = {k: v for k, v in kw.items() if k in keys}
+    x, w, b = t["x"].to(dev), t["w"].to(dev), t["bias"].to(dev)
+    good = Session(T, spec["H"], spec["E"], spec["K"], device=dev, gate_impl="umma", **skw)
+    good.run(x, w, b)
+    torch.cuda.synchronize()
+    assert good.status()[0] == 0
+    want = {k: getattr(good, k).clone() for k in ("expert_ids", "inverse_perm", "offsets", "combine_weights")}
+    stall = Session(T, spec["H"], spec["E"], spec["K"], device=dev, gate_impl="umma",
+                    flags=_cabi.FLAG_TEST_GATE_STALL, **skw)
+    stall.workspace = good.workspace  # the same workspace takes the failing call, then a good one
+    stall.run(x, w, b)
+    with pytest.raises(_cabi.MoeRdError) as err:
+        stall.status()
+    assert err.value.code == -9
+    ids = [int(v) for v in str(err.value).split("[")[1].split("]")[0].split(",")]
+    assert ids[0] == 1 and ids[1] in (102, 103, 112), ids
+    good.run(x, w, b)
+    torch.cuda.synchronize()
+    assert good.status()[0] == 0
+    for k, v in want.items():
+        assert torch.equal(getattr(good, k), v), k
