@@ -25,9 +25,6 @@
 #ifndef MOE_RD_ROUTE_SORTED
 #define MOE_RD_ROUTE_SORTED 1
 #endif
-#ifndef MOE_RD_ROUTE_THRESHOLD   // 1: find the K experts through a threshold and a short list instead of
-#define MOE_RD_ROUTE_THRESHOLD 0 //    rounds of arg-max (same results; measured no faster, see route_token)
-#endif
 
 namespace moe_rd {
 
@@ -75,24 +72,9 @@ __device__ __forceinline__ float ord_value(uint32_t k) {
 // every round broadcasting it out of a register picked by a chain of selects.
 // A selected key is removed by zeroing its image (0 = not eligible), so a round
 // costs one max pass, one index pass and one removal pass over the registers.
-//
-// s_cand: null, or kRouteCandWords words of shared memory owned by this warp.
-// Then the K experts are found without rounds where possible:
-//   1. every register row i (a slice of 32 consecutive experts, lane + 32*i) that
-//      still has eligible keys notes its q-th largest key, q = ceil(K / such rows);
-//      the smallest of these, tau, is a lower bound of the K-th largest key of the
-//      token, because at least K keys are >= tau;
-//   2. the keys >= tau (a dozen or so) are listed in expert order by ballot;
-//   3. lane c counts the listed keys that beat key c (larger, or equal and listed
-//      earlier, i.e. with a lower expert index): that count is its slot if < K.
-// "Larger key first, lower index on ties" is a total order, so this is the set
-// and order that the K rounds of arg-max produce.  If more than 32 keys reach
-// tau (long runs of equal keys) or fewer than K are eligible, the rounds decide.
-constexpr int kRouteCandWords = 3 * 32 + 2 * kMaxK;
-
 template <int EPL, bool FULL>
 __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)[EPL], int lane,
-                                            float* s_sc, int& mysel, float& myw, uint32_t* s_cand = nullptr) {
+                                            float* s_sc, int& mysel, float& myw) {
   float sc[EPL];
   uint32_t ok[EPL];  // ordered images of the selection keys; 0 = not eligible
   if (a.score_fn == MOE_RD_SCORE_SOFTMAX) {
@@ -227,80 +209,6 @@ __device__ __forceinline__ void route_token(const RouteArgs& a, const float (&z)
 
   float tot = 0.0f, myu = 0.0f;
   mysel = 0;
-  if (MOE_RD_ROUTE_THRESHOLD && s_cand != nullptr && EPL > 1) {
-    // rows that still have eligible keys, and the number of keys each notes
-    unsigned rows = 0u;
-#pragma unroll
-    for (int i = 0; i < EPL; ++i)
-      if (__any_sync(kFull, ok[i] != 0u)) rows |= 1u << i;
-    const int nrows = __popc(rows);
-    const int q = nrows > 0 ? (a.K + nrows - 1) / nrows : 99;
-    if (q <= 4) {
-      uint32_t tau = 0xffffffffu;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        if ((rows >> i) & 1u) {
-          uint32_t v = ok[i], m = 0u;
-          for (int r = 0; r < q; ++r) {
-            m = __reduce_max_sync(kFull, v);
-            if (r + 1 < q) {
-              // take ONE instance of the maximum out (equal keys count separately)
-              const unsigned holders = __ballot_sync(kFull, v == m);
-              if (lane == __ffs(holders) - 1) v = 0u;
-            }
-          }
-          tau = min(tau, m);
-        }
-      }
-      unsigned b[EPL];
-      int n = 0;
-#pragma unroll
-      for (int i = 0; i < EPL; ++i) {
-        b[i] = __ballot_sync(kFull, ok[i] >= tau && ok[i] != 0u);
-        n += __popc(b[i]);
-      }
-      if (n <= 32 && n >= a.K) {
-        uint32_t* s_k = s_cand;                                      // [32] listed keys, in expert order
-        int* s_e = reinterpret_cast<int*>(s_cand + 32);              // [32] their experts
-        float* s_v = reinterpret_cast<float*>(s_cand + 64);          // [32] their unbiased scores
-        int* s_sel = reinterpret_cast<int*>(s_cand + 96);            // [K] slots
-        float* s_u = reinterpret_cast<float*>(s_cand + 96 + kMaxK);  // [K]
-        __syncwarp();  // the previous token's readers are done
-        const unsigned below = (1u << lane) - 1u;
-        int base = 0;
-#pragma unroll
-        for (int i = 0; i < EPL; ++i) {
-          if ((b[i] >> lane) & 1u) {
-            const int pos = base + __popc(b[i] & below);
-            s_k[pos] = ok[i];
-            s_e[pos] = lane + 32 * i;
-            s_v[pos] = sc[i];
-          }
-          base += __popc(b[i]);
-        }
-        __syncwarp();
-        const uint32_t k = lane < n ? s_k[lane] : 0u;
-        int rank = 0;
-        for (int c = 0; c < n; ++c) {
-          const uint32_t k2 = s_k[c];
-          rank += (k2 > k || (k2 == k && c < lane)) ? 1 : 0;
-        }
-        if (lane < n && rank < a.K) {
-          s_sel[rank] = s_e[lane];
-          s_u[rank] = a.weight_from_key ? ord_value(k) : s_v[lane];
-        }
-        __syncwarp();
-        if (lane < a.K) {
-          mysel = s_sel[lane];
-          myu = s_u[lane];
-        }
-        for (int kk = 0; kk < a.K; ++kk) tot = __fadd_rn(tot, __shfl_sync(kFull, myu, kk));
-        const float wq = a.renorm ? __fdiv_rn(myu, fmaxf(tot, a.norm_min)) : myu;
-        myw = __fmul_rn(wq, a.routed_scale);
-        return;
-      }
-    }
-  }
   if (staged) {
     __syncwarp();  // the previous token's readers are done with s_sc
 #pragma unroll
