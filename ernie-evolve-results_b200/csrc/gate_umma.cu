@@ -70,6 +70,21 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// L2 policy for the loads of x: keep the lines if possible.  The row scatter reads x again right
+// after the routing front, and whatever part of x is still in L2 then does not come from HBM a
+// second time (measured on T=8192, H=7168: scatter 100.2 -> 97.2 us).
+__device__ __forceinline__ uint64_t policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_load_2d_keep(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                 uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y,
                                             uint32_t bar) {
   asm volatile(
@@ -144,6 +159,13 @@ __device__ __forceinline__ void cluster_sync_all() {
 // TMA load of one CTA of a pair; the bytes are counted on `bar`, a barrier of
 // the pair's leader CTA (cluster address).  No multicast: each CTA fetches
 // only what lands in its own shared memory.
+__device__ __forceinline__ void tma_load_2d_pair_keep(uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                      uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "l"(policy)
+      : "memory");
+}
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y,
                                                  uint32_t bar) {
   asm volatile(
@@ -313,6 +335,7 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      const uint64_t keep_x = policy_evict_last();
       int issued = 0;
       for (int i = 0; i < nkb && !a.no_loads; ++i) {
         const int s = i % a.stages;
@@ -326,8 +349,8 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
         mbar_expect_tx(fb, stage_bytes);
         unsigned char* st = smem + (size_t)s * stage_bytes;
         for (int h = 0; h < a.mh; ++h)
-          tma_load_2d(smem_u32(st + h * half_bytes), &map_x, (kb0 + i) * kBlockK,
-                      (mt * a.mh + h) * kBlockM, fb);
+          tma_load_2d_keep(smem_u32(st + h * half_bytes), &map_x, (kb0 + i) * kBlockK,
+                           (mt * a.mh + h) * kBlockM, fb, keep_x);
         if (a.w_mn_major) {
           // one [64 h][64 e] box per block of 64 experts, 8 KB apart
           for (int nb = 0; nb < a.E / 64; ++nb)
@@ -459,6 +482,7 @@ gate_umma_pair_kernel(const __grid_constant__ CUtensorMap map_x,
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      const uint64_t keep_x = policy_evict_last();
       int issued = 0;
       for (int i = 0; i < nkb && !a.no_loads; ++i) {
         const int s = i % a.stages;
@@ -472,7 +496,7 @@ gate_umma_pair_kernel(const __grid_constant__ CUtensorMap map_x,
         if (rank == 0) mbar_expect_tx(smem_u32(full_bar + s), 2u * stage_bytes);
         const uint32_t fb = map_to_cta(smem_u32(full_bar + s), 0u);
         unsigned char* st = smem + (size_t)s * stage_bytes;
-        tma_load_2d_pair(smem_u32(st), &map_x, (kb0 + i) * kBlockK, mt * kBlockM, fb);
+        tma_load_2d_pair_keep(smem_u32(st), &map_x, (kb0 + i) * kBlockK, mt * kBlockM, fb, keep_x);
         if (a.w_mn_major) {
           // this CTA's E/128 boxes of [64 h][64 e], 8 KB apart
           const int nbox = a.E / 128;
