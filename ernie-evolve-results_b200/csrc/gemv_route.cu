@@ -58,6 +58,21 @@ __device__ __forceinline__ u64 bf16x2_to_f32x2(uint32_t v) {
   return r;
 }
 
+// 16-byte load of x with an L2 evict-last policy: the row scatter reads x again right after this
+// kernel, and what is still in L2 then does not come from HBM a second time.
+__device__ __forceinline__ uint4 ld_x_keep(const uint4* p, u64 policy) {
+  uint4 v;
+  asm volatile("ld.global.nc.L2::cache_hint.v4.u32 {%0, %1, %2, %3}, [%4], %5;"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p), "l"(policy));
+  return v;
+}
+__device__ __forceinline__ u64 policy_evict_last() {
+  u64 p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+
 struct GemvArgs {
   const uint16_t* x;
   const void* w;
@@ -156,6 +171,7 @@ gemv_route_kernel(const GemvArgs g, const RouteArgs a) {
   // A unit = TPW consecutive tokens carried by one warp.  Block b owns the
   // contiguous unit range [U*b/B, U*(b+1)/B), so with B = the SM count every SM
   // gets the same work to within one unit.
+  const u64 keep_x = policy_evict_last();
   const int64_t units = (a.T + TPW - 1) / TPW;
   const int64_t ulo = units * blockIdx.x / gridDim.x;
   const int64_t uhi = units * (blockIdx.x + 1) / gridDim.x;
@@ -178,7 +194,7 @@ gemv_route_kernel(const GemvArgs g, const RouteArgs a) {
     for (int i = 0; i < TPW; ++i) xn[i] = make_uint4(0, 0, 0, 0);
     if (lane * 8 < g.H) {
 #pragma unroll
-      for (int i = 0; i < TPW; ++i) xn[i] = __ldg(xr[i] + lane);
+      for (int i = 0; i < TPW; ++i) xn[i] = ld_x_keep(xr[i] + lane, keep_x);
     }
     for (int c = 0; c < nchunk; ++c) {
       const int h0 = c * 256 + lane * 8;
@@ -187,7 +203,7 @@ gemv_route_kernel(const GemvArgs g, const RouteArgs a) {
       for (int i = 0; i < TPW; ++i) xv[i] = xn[i];
       if (c + 1 < nchunk && h0 + 256 < g.H) {
 #pragma unroll
-        for (int i = 0; i < TPW; ++i) xn[i] = __ldg(xr[i] + ((h0 + 256) >> 3));
+        for (int i = 0; i < TPW; ++i) xn[i] = ld_x_keep(xr[i] + ((h0 + 256) >> 3), keep_x);
       }
       if (h0 < g.H) {
         const ulonglong2* wc = s_w + (size_t)c * 4 * (EB / 2) * 32 + lane;
