@@ -78,6 +78,10 @@ cudaError_t launch_scatter(const moe_rd_params& p, const moe_rd_buffers& b, cons
                            const int32_t* ids, const int32_t* tile_base, const int32_t* counts,
                            int32_t* status, int32_t* dense, const int32_t* group_counts, cudaStream_t s,
                            cudaEvent_t after_positions = nullptr);
+bool fused_front_eligible(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan);
+cudaError_t launch_gate_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan, void* wt,
+                              int32_t* ids, int32_t* tile_counts, int32_t* group_counts, int32_t* status,
+                              cudaStream_t s);
 bool umma_available();
 bool gemv_eligible(const moe_rd_params& p);
 void count_launch(int n = 1);

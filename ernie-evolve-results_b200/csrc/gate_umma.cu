@@ -17,6 +17,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "route_lane.cuh"
 
 namespace moe_rd {
 namespace {
@@ -36,6 +37,9 @@ constexpr uint32_t kSpinLimit = 1u << 20;
 #endif
 #ifndef MOE_RD_UMMA_SMEM_KB_TWO_CTA   // ... when two CTAs share it
 #define MOE_RD_UMMA_SMEM_KB_TWO_CTA 100
+#endif
+#ifndef MOE_RD_FUSED_FRONT   // 0: never fuse the routing into the gate kernel (tuning/validation)
+#define MOE_RD_FUSED_FRONT 1
 #endif
 #ifndef MOE_RD_UMMA_TWO_CTA_MAX_E     // largest E for which two CTAs per SM are targeted
 #define MOE_RD_UMMA_TWO_CTA_MAX_E 128
@@ -563,6 +567,320 @@ gate_umma_pair_kernel(const __grid_constant__ CUtensorMap map_x,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Gate product AND routing in one kernel, for shapes with several 128-token
+// tiles per SM, at most 128 product columns and no split over K: the logits
+// never leave the SM.  A CTA walks its tiles (b, b + grid, ...); the accumulator
+// alternates between two TMEM buffers, so that while the tensor core works on
+// tile i+1 the other warps route tile i:
+//   warp 0      TMA producer (x tile + W tile per 64-wide K block, one ring over all tiles)
+//   warp 1      MMA issuer; tmem_full[buf] when a tile's product is complete
+//   warps 2-5   drain: TMEM row -> shared-memory row (raw product columns), tmem_empty[buf]
+//   warps 6-31  routing: one token per warp at a time from the shared rows
+//               (route_token_c: consecutive experts per lane; the hi/lo columns of an
+//               fp32 weight are folded here), ids / weights / pair counts
+// Replaces cublasGemmEx + topk_kernel of the reference (kernel.cu:4327-4339,
+// 1829-1920) without the router_logits round trip through memory in between
+// (they are written only on request).  Every wait is bounded; a role that gives
+// up raises the abort flag and keeps passing the named barriers of its group so
+// that nobody is left waiting for it.
+// ---------------------------------------------------------------------------
+constexpr int kFusedThreads = 1024;
+constexpr int kRouteWarps0 = 6;                                    // first routing warp
+constexpr int kFusedRouteWarps = kFusedThreads / 32 - kRouteWarps0;  // 26
+constexpr int kFusedRouteThreads = kFusedRouteWarps * 32;
+
+struct FusedArgs {
+  RouteArgs r;          // routing parameters and outputs; r.fold: the rows hold 2E columns
+  int32_t* status;
+  int64_t T;
+  int N;                // product columns: E, or 2E
+  int kblocks, stages, w_mn_major;
+  int ntiles;           // 128-token tiles
+  int ncount_tiles;     // kTile-token counting tiles
+  uint32_t spin_limit;
+  int no_loads;
+};
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
+template <int EPL>
+__global__ void __launch_bounds__(kFusedThreads, 1)
+gate_route_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+                  const FusedArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t a_bytes = kBlockM * kBlockK * 2;
+  const uint32_t b_bytes = (uint32_t)a.N * kBlockK * 2;
+  const uint32_t stage_bytes = a_bytes + b_bytes;
+  const uint32_t row_pitch = (uint32_t)a.N * 4u + 16u;  // a 16-byte skew keeps a warp's 16-byte row stores apart
+  unsigned char* rows = smem + (size_t)a.stages * stage_bytes;               // [128][row_pitch] logits of one tile
+  int* s_cnt = reinterpret_cast<int*>(rows + (size_t)kBlockM * row_pitch);   // [2][E] pairs per counting tile half
+  uint32_t* s_cand = reinterpret_cast<uint32_t*>(s_cnt + 2 * a.r.E);         // [route warps][kLaneCandWords]
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(s_cand + kFusedRouteWarps * kLaneCandWords);
+  uint64_t* empty_bar = full_bar + a.stages;
+  uint64_t* tmem_full = empty_bar + a.stages;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;         // [2]
+  uint64_t* rows_full = tmem_empty + 2;         // [1]
+  uint64_t* rows_empty = rows_full + 1;         // [1]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rows_empty + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_trigger();
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < a.stages; ++s) {
+      mbar_init(smem_u32(full_bar + s), 1);
+      mbar_init(smem_u32(empty_bar + s), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(smem_u32(tmem_full + i), 1);
+      mbar_init(smem_u32(tmem_empty + i), 128);
+    }
+    mbar_init(smem_u32(rows_full), 128);
+    mbar_init(smem_u32(rows_empty), kFusedRouteWarps);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  const uint32_t tmem_cols = 2u * (uint32_t)a.N <= 32u ? 32u : 2u * (uint32_t)a.N <= 64u ? 64u
+                             : 2u * (uint32_t)a.N <= 128u ? 128u : 256u;
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                 "r"(tmem_cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i < 2 * a.r.E; i += kFusedThreads) s_cnt[i] = 0;
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+  const int my_tiles = (a.ntiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;  // b, b+G, ...
+
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_x) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+      const uint64_t keep_x = policy_evict_last();
+      int issued = 0;
+      bool ok = true;
+      for (int it = 0; it < my_tiles && ok && !a.no_loads; ++it) {
+        const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+        for (int kb = 0; kb < a.kblocks; ++kb) {
+          const int s = issued % a.stages;
+          const uint32_t use = (uint32_t)(issued / a.stages);
+          if (!mbar_wait(smem_u32(empty_bar + s), (use & 1u) ^ 1u, abort_flag, a.spin_limit)) {
+            if (!*abort_flag) report(a.status, 121, tile, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          const uint32_t fb = smem_u32(full_bar + s);
+          mbar_expect_tx(fb, stage_bytes);
+          unsigned char* st = smem + (size_t)s * stage_bytes;
+          tma_load_2d_keep(smem_u32(st), &map_x, kb * kBlockK, tile * kBlockM, fb, keep_x);
+          if (a.w_mn_major) {
+            for (int nb = 0; nb < a.N / 64; ++nb)
+              tma_load_2d(smem_u32(st + a_bytes + nb * 8192), &map_w, nb * 64, kb * kBlockK, fb);
+          } else {
+            tma_load_2d(smem_u32(st + a_bytes), &map_w, kb * kBlockK, 0, fb);
+          }
+          ++issued;
+        }
+      }
+      if (*abort_flag) {
+        // do not leave while copies into this CTA's shared memory are in flight
+        volatile int never = 0;
+        for (int j = issued > a.stages ? issued - a.stages : 0; j < issued; ++j)
+          mbar_wait(smem_u32(full_bar + j % a.stages), (uint32_t)(j / a.stages) & 1u, &never);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.N >> 3) << 17) |
+                             ((uint32_t)(kBlockM >> 4) << 24) | (a.w_mn_major ? (1u << 16) : 0u);
+      int consumed = 0;
+      bool ok = true;
+      for (int it = 0; it < my_tiles && ok; ++it) {
+        const int buf = it & 1;
+        const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+        // the drain warps have emptied this accumulator (its previous tile, two tiles ago)
+        if (!mbar_wait(smem_u32(tmem_empty + buf), ((uint32_t)(it >> 1) & 1u) ^ 1u, abort_flag, a.spin_limit)) {
+          if (!*abort_flag) report(a.status, 122, tile, it);
+          *abort_flag = 1;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        for (int kb = 0; kb < a.kblocks; ++kb) {
+          const int s = consumed % a.stages;
+          const uint32_t use = (uint32_t)(consumed / a.stages);
+          if (!mbar_wait(smem_u32(full_bar + s), use & 1u, abort_flag, a.spin_limit)) {
+            if (!*abort_flag) report(a.status, 123, tile, kb);
+            *abort_flag = 1;
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          unsigned char* st = smem + (size_t)s * stage_bytes;
+          const uint64_t da = make_desc(smem_u32(st));
+          const uint64_t db = a.w_mn_major ? make_desc_mn(smem_u32(st + a_bytes), 8192u)
+                                           : make_desc(smem_u32(st + a_bytes));
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);
+            const uint64_t step_b = a.w_mn_major ? (uint64_t)((k * 2048) >> 4) : step;
+            umma_f16(tmem_base + (uint32_t)(buf * a.N), da + step, db + step_b, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          umma_commit(smem_u32(empty_bar + s));
+          ++consumed;
+        }
+        if (ok) umma_commit(smem_u32(tmem_full + buf));
+      }
+    }
+  } else if (warp < kRouteWarps0) {
+    // ---- drain warps: TMEM lane = token row of the tile
+    const int q = warp & 3;
+    bool gave_up = false;
+    for (int it = 0; it < my_tiles; ++it) {
+      const int buf = it & 1;
+      const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+      if (!gave_up) {
+        bool ok = mbar_wait(smem_u32(tmem_full + buf), (uint32_t)(it >> 1) & 1u, abort_flag, a.spin_limit);
+        // the routing warps are done with the rows of the previous tile
+        ok = ok && mbar_wait(smem_u32(rows_empty), ((uint32_t)it & 1u) ^ 1u, abort_flag, a.spin_limit);
+        ok = __all_sync(kFull, ok);
+        if (!ok) {
+          if (lane == 0 && !*abort_flag) report(a.status, 124, tile, it);
+          *abort_flag = 1;
+          gave_up = true;
+        }
+      }
+      if (gave_up) continue;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      unsigned char* my_row = rows + (size_t)(q * 32 + lane) * row_pitch;
+      for (int c = 0; c < a.N; c += 32) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * a.N + c);
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+              "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+              "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+              "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+              "=r"(r[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        uint4* o4 = reinterpret_cast<uint4*>(my_row + (size_t)c * 4);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o4[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+      }
+      // the accumulator may be overwritten, and the rows may be read
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(smem_u32(tmem_empty + buf));
+      mbar_arrive(smem_u32(rows_full));
+    }
+  } else {
+    // ---- routing warps
+    const int rw = warp - kRouteWarps0;
+    const RouteArgs& ra = a.r;
+    uint32_t* my_cand = s_cand + rw * kLaneCandWords;
+    bool gave_up = false;
+    for (int it = 0; it < my_tiles; ++it) {
+      const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+      const int64_t t0 = (int64_t)tile * kBlockM;
+      if (!gave_up) {
+        bool ok = mbar_wait(smem_u32(rows_full), (uint32_t)it & 1u, abort_flag, a.spin_limit);
+        ok = __all_sync(kFull, ok);
+        if (!ok) {
+          if (lane == 0 && !*abort_flag) report(a.status, 125, tile, it);
+          *abort_flag = 1;
+          gave_up = true;
+        }
+      }
+      if (!gave_up) {
+        for (int tk = rw; tk < kBlockM; tk += kFusedRouteWarps) {
+          const int64_t t = t0 + tk;
+          if (t >= a.T) break;
+          // this lane's experts: EPL consecutive columns (plus the lo columns of an fp32 weight)
+          const float* row = reinterpret_cast<const float*>(rows + (size_t)tk * row_pitch) + EPL * lane;
+          float z[EPL];
+          if (EPL == 2) {
+            const float2 v = *reinterpret_cast<const float2*>(row);
+            z[0] = v.x; z[1] = v.y;
+          } else {
+#pragma unroll
+            for (int v4 = 0; v4 < EPL / 4; ++v4) {
+              const float4 v = reinterpret_cast<const float4*>(row)[v4];
+              z[4 * v4] = v.x; z[4 * v4 + 1] = v.y; z[4 * v4 + 2] = v.z; z[4 * v4 + 3] = v.w;
+            }
+          }
+          if (ra.fold) {
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) z[j] = __fadd_rn(z[j], row[ra.E + j]);
+          }
+          if (ra.logit_bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) z[j] = __fadd_rn(z[j], __ldg(ra.logit_bias + EPL * lane + j));
+          }
+          if (ra.logits_out != nullptr) {
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) ra.logits_out[(size_t)t * ra.E + EPL * lane + j] = z[j];
+          }
+          int mysel;
+          float myw;
+          route_token_c<EPL>(ra, z, lane, my_cand, mysel, myw);
+          if (lane < ra.K) {
+            const size_t o = (size_t)t * ra.K + lane;
+            ra.ids[o] = mysel;
+            ra.weights[o] = myw;
+            atomicAdd(s_cnt + (tk >> 6) * ra.E + mysel, 1);  // kTile = 64: two counting tiles per 128-token tile
+          }
+        }
+      }
+      // every routing warp passes both barriers of every tile, also after it gave up
+      named_bar_sync(1, kFusedRouteThreads);
+      if (!gave_up) {
+        if (lane == 0) mbar_arrive(smem_u32(rows_empty));
+        // the tile's pair counts: stored per (counting tile, expert) - this CTA owns both counting
+        // tiles whole - and added per (group of counting tiles, expert)
+        const int rt = (int)threadIdx.x - kRouteWarps0 * 32;
+        for (int i = rt; i < 2 * ra.E; i += kFusedRouteThreads) {
+          const int half = i / ra.E, e = i - half * ra.E;
+          const int ct = tile * 2 + half;
+          const int v = s_cnt[i];
+          s_cnt[i] = 0;
+          if (ct < a.ncount_tiles) {
+            ra.tile_counts[(size_t)ct * ra.E + e] = v;
+            if (v) atomicAdd(ra.group_counts + (size_t)(ct / kTileGroup) * ra.E + e, v);
+          }
+        }
+      }
+      named_bar_sync(1, kFusedRouteThreads);
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 0) {
+    __syncwarp();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(tmem_cols)
+                 : "memory");
+  }
+}
+
+
 // W[H,E] -> Wt[E,H] (bf16), 32x32 tiles through shared memory.
 __global__ void __launch_bounds__(256) transpose_w_kernel(const uint16_t* __restrict__ w,
                                                           uint16_t* __restrict__ wt, int H, int E) {
@@ -684,12 +1002,108 @@ size_t umma_smem_bytes(int E, int stages, int mh) {
 
 bool umma_available() { return true; }
 
+int device_sms();
+static int device_sms_cached() { return device_sms(); }
+void fill_route_args(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan, const float* logits,
+                     int32_t* ids, int32_t* tile_base, int32_t* counts, RouteArgs* a);
+
 cudaError_t init_umma_attributes() {
   cudaError_t e = cudaFuncSetAttribute(gate_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                        227 * 1024);
   if (e != cudaSuccess) return e;
-  return cudaFuncSetAttribute(gate_umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                              227 * 1024);
+  e = cudaFuncSetAttribute(gate_umma_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e != cudaSuccess) return e;
+  e = cudaFuncSetAttribute(gate_route_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+  if (e != cudaSuccess) return e;
+  return cudaFuncSetAttribute(gate_route_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+}
+
+static_assert(kTile == 64, "gate_route_kernel keeps two counting tiles per 128-token tile");
+
+// Shared memory of gate_route_kernel with `stages` ring stages.
+static size_t fused_smem_bytes(int N, int E, int stages) {
+  return (size_t)stages * (kBlockM * kBlockK * 2 + N * kBlockK * 2) + (size_t)kBlockM * (N * 4 + 16) +
+         (size_t)2 * E * 4 + (size_t)kFusedRouteWarps * kLaneCandWords * 4 + (size_t)(2 * stages + 6) * 8 + 16 + 1024;
+}
+
+// Whether the fused gate + routing kernel takes this problem: no split over K, at most 128 product
+// columns, E of 64 or 128 (consecutive experts per lane), enough 128-token tiles that most CTAs get two
+// or more (the routing of one tile then overlaps the K loop of the next), and biases / logits that can
+// be read as 16-byte vectors.
+bool fused_front_eligible(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan) {
+  if (!MOE_RD_FUSED_FRONT || plan.gate != MOE_RD_GATE_UMMA || plan.ksplit != 1 || plan.umma_pair) return false;
+  if (plan.umma_n > 128 || (p.E != 64 && p.E != 128)) return false;
+  if (!lane_route_supported(p.E, p.K, p.n_groups, p.topk_groups, p.group_topk)) return false;
+  const int64_t ntiles = (p.T + kBlockM - 1) / kBlockM;
+  if (ntiles < (int64_t)device_sms_cached() * 5 / 4) return false;
+  const auto mis = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) != 0; };
+  if (mis(b.logit_bias) || mis(b.select_bias) || mis(b.router_logits)) return false;
+  return fused_smem_bytes(plan.umma_n, p.E, 3) <= 227 * 1024;
+}
+
+cudaError_t launch_gate_route(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan, void* wt,
+                              int32_t* ids, int32_t* tile_counts, int32_t* group_counts, int32_t* status,
+                              cudaStream_t s) {
+  const int N = plan.umma_n;
+  const uint16_t* w_eh = static_cast<const uint16_t*>(b.gate_w);
+  const bool mn_major = !plan.umma_fold && p.w_layout == MOE_RD_W_LAYOUT_HE && p.E % 64 == 0;
+  if (plan.umma_fold) {
+    const float* wf = static_cast<const float*>(b.gate_w);
+    if (p.w_layout == MOE_RD_W_LAYOUT_EH) {
+      const size_t n4 = (size_t)p.E * p.H / 4;
+      const unsigned blocks = (unsigned)((n4 + 255) / 256 < 1184 ? (n4 + 255) / 256 : 1184);
+      wsplit_eh_kernel<<<blocks, 256, 0, s>>>(wf, static_cast<uint16_t*>(wt), p.H, p.E);
+    } else {
+      const dim3 grid((unsigned)((p.H + 31) / 32), (unsigned)((p.E + 31) / 32));
+      wsplit_he_kernel<<<grid, 256, 0, s>>>(wf, static_cast<uint16_t*>(wt), p.H, p.E);
+    }
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    w_eh = static_cast<const uint16_t*>(wt);
+  } else if (p.w_layout == MOE_RD_W_LAYOUT_HE && !mn_major) {
+    const dim3 grid((unsigned)((p.H + 31) / 32), (unsigned)((p.E + 31) / 32));
+    transpose_w_kernel<<<grid, 256, 0, s>>>(static_cast<const uint16_t*>(b.gate_w), static_cast<uint16_t*>(wt),
+                                            p.H, p.E);
+    count_launch();
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    w_eh = static_cast<const uint16_t*>(wt);
+  }
+  CUtensorMap map_x, map_w;
+  if (!make_map(&map_x, b.x, (uint64_t)p.T, (uint64_t)p.H, kBlockM)) return cudaErrorInvalidValue;
+  if (mn_major ? !make_map(&map_w, b.gate_w, (uint64_t)p.H, (uint64_t)p.E, 64u)
+               : !make_map(&map_w, w_eh, (uint64_t)N, (uint64_t)p.H, (uint32_t)N))
+    return cudaErrorInvalidValue;
+  FusedArgs a;
+  fill_route_args(p, b, plan, nullptr, ids, tile_counts, nullptr, &a.r);
+  a.r.group_counts = group_counts;
+  a.r.fold = plan.umma_fold;
+  a.r.logit_bias = b.logit_bias;
+  a.r.logits_out = b.router_logits;
+  a.status = status;
+  a.T = p.T;
+  a.N = N;
+  a.kblocks = p.H / kBlockK;
+  a.w_mn_major = mn_major ? 1 : 0;
+  a.ntiles = (int)((p.T + kBlockM - 1) / kBlockM);
+  a.ncount_tiles = plan.ntiles;
+  a.no_loads = (p.flags & MOE_RD_FLAG_TEST_GATE_STALL) ? 1 : 0;
+  a.spin_limit = a.no_loads ? 256u : kSpinLimit;
+  int stages = 8;
+  while (stages > 2 && fused_smem_bytes(N, p.E, stages) > 227 * 1024) --stages;
+  a.stages = stages;
+  // every CTA the same number of tiles: grid = tiles / (tiles per CTA), rounded up
+  const int sms = device_sms_cached();
+  const int per = (a.ntiles + sms - 1) / sms;
+  const unsigned grid = (unsigned)((a.ntiles + per - 1) / per);
+  const size_t smem = fused_smem_bytes(N, p.E, stages);
+  if (p.E == 64)
+    gate_route_kernel<2><<<grid, kFusedThreads, smem, s>>>(map_x, map_w, a);
+  else
+    gate_route_kernel<4><<<grid, kFusedThreads, smem, s>>>(map_x, map_w, a);
+  count_launch();
+  return cudaGetLastError();
 }
 
 cudaError_t launch_gate_umma(const moe_rd_params& p, const moe_rd_buffers& b, const Plan& plan,

@@ -252,12 +252,18 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   // first tiles load), which saves the separate memset node.
   // (not in the time-out test: there a CTA may record its status within microseconds of the start,
   // before the first CTA has cleared the block)
-  const bool gate_clears = plan.gate == MOE_RD_GATE_UMMA && p->T > 0 && !(p->flags & MOE_RD_FLAG_TEST_GATE_STALL);
+  // Gate product and routing in one kernel where that pays (several token tiles per SM): its routing
+  // warps add to the group counts while other CTAs are still starting, so the clear comes first.
+  const bool fused = p->T > 0 && fused_front_eligible(*p, *b, plan);
+  const bool gate_clears = plan.gate == MOE_RD_GATE_UMMA && p->T > 0 && !fused &&
+                           !(p->flags & MOE_RD_FLAG_TEST_GATE_STALL);
   if (!gate_clears) MOE_RD_CUDA(cudaMemsetAsync(ws + w.status, 0, w.zero_bytes, s));
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[0], s));
   if (p->T > 0) {
     if (plan.gate == MOE_RD_GATE_SIMT) {
       MOE_RD_CUDA(launch_gate_simt(*p, *b, logits, s));
+    } else if (fused) {
+      MOE_RD_CUDA(launch_gate_route(*p, *b, plan, ws + w.wt, ids, tile_base, group_counts, status, s));
     } else if (plan.gate == MOE_RD_GATE_UMMA) {
       MOE_RD_CUDA(launch_gate_umma(*p, *b, plan, ws + w.wt,
                                    reinterpret_cast<float*>(ws + w.partial), logits, status,
@@ -266,7 +272,9 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   }
   if (ev) MOE_RD_CUDA(cudaEventRecord(ev[1], s));
   if (p->T > 0) {
-    if (plan.gate == MOE_RD_GATE_GEMV)
+    if (fused) {
+      // routed inside the gate kernel
+    } else if (plan.gate == MOE_RD_GATE_GEMV)
       MOE_RD_CUDA(launch_gemv_route(*p, *b, plan, b->router_logits, ids, tile_base, counts, status + 16, s));
     else if (plan.gate == MOE_RD_GATE_UMMA)
       MOE_RD_CUDA(launch_route_splits(*p, *b, plan, reinterpret_cast<float*>(ws + w.partial),

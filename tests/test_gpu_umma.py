@@ -159,3 +159,50 @@ def test_a_wait_that_runs_out_is_reported_and_the_workspace_stays_usable(name, T
     assert good.status()[0] == 0
     for k, v in want.items():
         assert torch.equal(getattr(good, k), v), k
+
+
+# ------------------------------- gate product and routing in one kernel --
+@pytest.mark.parametrize("name,T", [("c3", 24100), ("ref", 25000)])
+def test_fused_gate_and_routing_kernel(name, T):
+    """With several 128-token tiles per SM, at most 128 product columns and no split over K the
+    routing runs inside the gate kernel (logits stay on the SM, written out only on request).
+    Ragged token counts; bf16 weights (c3: logit bias, capacity drops) and fp32 weights through
+    the hi/lo split folded by the routing warps (the reference's shape with more tokens)."""
+    H = 2048 if name == "c3" else 1024
+    t, kw = workloads.make(name, T=T, H=H)
+    if name == "c3":
+        kw = dict(kw, capacity=int(np.ceil(1.25 * T * kw["top_k"] / 128)))
+    a, _ = staged_check(t, kw)
+    b = _util.to_np(_util.run_gpu(t, kw, gate_impl="umma"))  # without the logits output
+    np.testing.assert_array_equal(a["expert_ids"], b["expert_ids"])
+    np.testing.assert_array_equal(a["inverse_perm"], b["inverse_perm"])
+    np.testing.assert_array_equal(a["combine_weights"].view(np.uint32), b["combine_weights"].view(np.uint32))
+
+
+def test_fused_kernel_time_out_path():
+    from moe_rd import _cabi
+    from moe_rd.runtime import Session
+    dev = torch.device("cuda:0")
+    T = 24100  # enough 128-token tiles for the fused kernel to be chosen
+    t, kw = workloads.make("c3", T=T, H=512)
+    kw = dict(kw, capacity=int(np.ceil(1.25 * T * 8 / 128)))
+    keys = ("score_fn", "bias_mode", "renorm", "capacity")
+    skw = {k: v for k, v in kw.items() if k in keys}
+    x, w, b = t["x"].to(dev), t["w"].to(dev), t["bias"].to(dev)
+    good = Session(T, 512, 128, 8, device=dev, gate_impl="umma", **skw)
+    good.run(x, w, b)
+    torch.cuda.synchronize()
+    assert good.status()[0] == 0
+    want = {k: getattr(good, k).clone() for k in ("expert_ids", "inverse_perm", "offsets", "combine_weights")}
+    stall = Session(T, 512, 128, 8, device=dev, gate_impl="umma", flags=_cabi.FLAG_TEST_GATE_STALL, **skw)
+    stall.workspace = good.workspace
+    stall.run(x, w, b)
+    with pytest.raises(_cabi.MoeRdError) as err:
+        stall.status()
+    ids = [int(v) for v in str(err.value).split("[")[1].split("]")[0].split(",")]
+    assert ids[0] == 1 and ids[1] in (122, 123, 124, 125), ids
+    good.run(x, w, b)
+    torch.cuda.synchronize()
+    assert good.status()[0] == 0
+    for k, v in want.items():
+        assert torch.equal(getattr(good, k), v), k
