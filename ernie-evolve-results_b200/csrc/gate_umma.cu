@@ -575,8 +575,9 @@ gate_umma_pair_kernel(const __grid_constant__ CUtensorMap map_x,
 // tile i+1 the other warps route tile i:
 //   warp 0      TMA producer (x tile + W tile per 64-wide K block, one ring over all tiles)
 //   warp 1      MMA issuer; tmem_full[buf] when a tile's product is complete
-//   warps 2-5   drain: TMEM row -> shared-memory row (raw product columns), tmem_empty[buf]
-//   warps 6-31  routing: one token per warp at a time from the shared rows
+//   warps 2-5   drain: TMEM row -> shared-memory row (raw product columns), tmem_empty[buf];
+//               then they route with the others
+//   warps 2-31  routing: one token per warp at a time from the shared rows
 //               (route_token_c: consecutive experts per lane; the hi/lo columns of an
 //               fp32 weight are folded here), ids / weights / pair counts
 // Replaces cublasGemmEx + topk_kernel of the reference (kernel.cu:4327-4339,
@@ -586,8 +587,9 @@ gate_umma_pair_kernel(const __grid_constant__ CUtensorMap map_x,
 // that nobody is left waiting for it.
 // ---------------------------------------------------------------------------
 constexpr int kFusedThreads = 1024;
-constexpr int kRouteWarps0 = 6;                                    // first routing warp
-constexpr int kFusedRouteWarps = kFusedThreads / 32 - kRouteWarps0;  // 26
+constexpr int kRouteWarps0 = 2;                                    // first routing warp (2-5 drain first)
+constexpr int kDrainWarps = 4;
+constexpr int kFusedRouteWarps = kFusedThreads / 32 - kRouteWarps0;  // 30
 constexpr int kFusedRouteThreads = kFusedRouteWarps * 32;
 
 struct FusedArgs {
@@ -628,8 +630,7 @@ gate_route_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
   uint64_t* tmem_full = empty_bar + a.stages;   // [2]
   uint64_t* tmem_empty = tmem_full + 2;         // [2]
   uint64_t* rows_full = tmem_empty + 2;         // [1]
-  uint64_t* rows_empty = rows_full + 1;         // [1]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rows_empty + 1);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(rows_full + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -644,7 +645,6 @@ gate_route_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       mbar_init(smem_u32(tmem_empty + i), 128);
     }
     mbar_init(smem_u32(rows_full), 128);
-    mbar_init(smem_u32(rows_empty), kFusedRouteWarps);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -744,61 +744,55 @@ gate_route_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
         if (ok) umma_commit(smem_u32(tmem_full + buf));
       }
     }
-  } else if (warp < kRouteWarps0) {
-    // ---- drain warps: TMEM lane = token row of the tile
-    const int q = warp & 3;
-    bool gave_up = false;
-    for (int it = 0; it < my_tiles; ++it) {
-      const int buf = it & 1;
-      const int tile = (int)blockIdx.x + it * (int)gridDim.x;
-      if (!gave_up) {
-        bool ok = mbar_wait(smem_u32(tmem_full + buf), (uint32_t)(it >> 1) & 1u, abort_flag, a.spin_limit);
-        // the routing warps are done with the rows of the previous tile
-        ok = ok && mbar_wait(smem_u32(rows_empty), ((uint32_t)it & 1u) ^ 1u, abort_flag, a.spin_limit);
-        ok = __all_sync(kFull, ok);
-        if (!ok) {
-          if (lane == 0 && !*abort_flag) report(a.status, 124, tile, it);
-          *abort_flag = 1;
-          gave_up = true;
-        }
-      }
-      if (gave_up) continue;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      unsigned char* my_row = rows + (size_t)(q * 32 + lane) * row_pitch;
-      for (int c = 0; c < a.N; c += 32) {
-        uint32_t r[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * a.N + c);
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-              "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
-              "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
-              "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-              "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
-              "=r"(r[31])
-            : "r"(taddr)
-            : "memory");
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        uint4* o4 = reinterpret_cast<uint4*>(my_row + (size_t)c * 4);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) o4[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-      }
-      // the accumulator may be overwritten, and the rows may be read
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(smem_u32(tmem_empty + buf));
-      mbar_arrive(smem_u32(rows_full));
-    }
   } else {
-    // ---- routing warps
+    // ---- warps 2..31: (warps 2-5: drain the accumulator of the tile, then) route the tile
+    const bool drains = warp < kRouteWarps0 + kDrainWarps;
+    const int q = warp & 3;  // TMEM lane quarter a drain warp may touch
     const int rw = warp - kRouteWarps0;
     const RouteArgs& ra = a.r;
     uint32_t* my_cand = s_cand + rw * kLaneCandWords;
     bool gave_up = false;
     for (int it = 0; it < my_tiles; ++it) {
+      const int buf = it & 1;
       const int tile = (int)blockIdx.x + it * (int)gridDim.x;
       const int64_t t0 = (int64_t)tile * kBlockM;
+      if (drains && !gave_up) {
+        // (the rows of the previous tile are free: this warp passed the barriers of its routing)
+        bool ok = mbar_wait(smem_u32(tmem_full + buf), (uint32_t)(it >> 1) & 1u, abort_flag, a.spin_limit);
+        ok = __all_sync(kFull, ok);
+        if (!ok) {
+          if (lane == 0 && !*abort_flag) report(a.status, 124, tile, it);
+          *abort_flag = 1;
+          gave_up = true;
+        } else {
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          unsigned char* my_row = rows + (size_t)(q * 32 + lane) * row_pitch;
+          for (int c = 0; c < a.N; c += 32) {
+            uint32_t r[32];
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * a.N + c);
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                  "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]),
+                  "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]),
+                  "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                  "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]),
+                  "=r"(r[31])
+                : "r"(taddr)
+                : "memory");
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            uint4* o4 = reinterpret_cast<uint4*>(my_row + (size_t)c * 4);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o4[i] = make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
+          }
+          // the accumulator may be overwritten, and the rows may be read
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(smem_u32(tmem_empty + buf));
+          mbar_arrive(smem_u32(rows_full));
+        }
+      }
       if (!gave_up) {
         bool ok = mbar_wait(smem_u32(rows_full), (uint32_t)it & 1u, abort_flag, a.spin_limit);
         ok = __all_sync(kFull, ok);
@@ -848,10 +842,9 @@ gate_route_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           }
         }
       }
-      // every routing warp passes both barriers of every tile, also after it gave up
+      // every one of these warps passes both barriers of every tile, also after it gave up
       named_bar_sync(1, kFusedRouteThreads);
       if (!gave_up) {
-        if (lane == 0) mbar_arrive(smem_u32(rows_empty));
         // the tile's pair counts: stored per (counting tile, expert) - this CTA owns both counting
         // tiles whole - and added per (group of counting tiles, expert)
         const int rt = (int)threadIdx.x - kRouteWarps0 * 32;
@@ -866,6 +859,7 @@ gate_route_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           }
         }
       }
+      // after this barrier the rows may be overwritten by the drain warps and the histogram is clear
       named_bar_sync(1, kFusedRouteThreads);
     }
   }
