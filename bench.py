@@ -478,7 +478,7 @@ def run_sweep(dev, flush, names, peak, steps=10):
     torch.mm of x [T,H] bf16 with the bf16 operand the gate kernel consumes ([H,E], or [H,2E] hi|lo columns
     for an fp32 weight, the reference's own GEMM shape, kernel.cu:4327-4339), fp32 output."""
     import torch
-    from moe_rd import workloads
+    from moe_rd import workloads, _cabi
     from moe_rd.runtime import Session
     other, cmp_ = {}, {}
     for name in names + ["c4"]:
@@ -515,8 +515,20 @@ def run_sweep(dev, flush, names, peak, steps=10):
                            "algorithmic_bytes": nbytes, "achieved_gbs": gbs, "frac_of_measured": gbs / peak,
                            "frac_of_8000": gbs / 8000.0,
                            "stage_ms": {"gate": st[0], "route": st[1], "positions": st[3], "scatter": st[4]},
+                           "stage_note": "where gate and routing are one kernel its time is under gate",
                            "steps": steps}
         if E >= 64:
+            # the gate product alone: gate and routing kept in two kernels for this leg
+            sep = Session(T, H, E, K, device=dev, w_dtype=w.dtype, flags=_cabi.FLAG_SEPARATE_GATE_AND_ROUTING,
+                          **session_kwargs(kw))
+            for _ in range(3):
+                sep.run(x, w, bias)
+            gate_ms = []
+            for _ in range(5):
+                flush.zero_()
+                gate_ms.append(sep.run_timed(x, w, bias)[0])
+            gate_us = statistics.mean(gate_ms) * 1e3
+            del sep
             if w.dtype == torch.float32:
                 wf = w if kw.get("w_layout", "HE") == "HE" else w.t()
                 hi = wf.to(torch.bfloat16)
@@ -542,7 +554,7 @@ def run_sweep(dev, flush, names, peak, steps=10):
                 e_.record()
             torch.cuda.synchronize()
             cub = statistics.mean(s_.elapsed_time(e_) for s_, e_ in evc) * 1e3
-            cmp_[name] = {"shape": f"[{T},{H}]x[{H},{wb.shape[1]}]", "ours_us": st[0] * 1e3, "cublas_us": cub,
+            cmp_[name] = {"shape": f"[{T},{H}]x[{H},{wb.shape[1]}]", "ours_us": gate_us, "cublas_us": cub,
                           "cublas_out": out_kind,
                           "note": "both are CUDA-event pairs around the launch(es) with a cold L2; ours includes the "
                                   "per-call weight split for fp32 weights and writes split-K partials"}

@@ -114,7 +114,9 @@ static int validate(const moe_rd_params* p) {
   if (p->scatter_impl < MOE_RD_SCATTER_AUTO || p->scatter_impl > MOE_RD_SCATTER_NONE)
     return MOE_RD_E_ENUM;
   if (p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128 && p->H % 128 != 0) return MOE_RD_E_SHAPE;
-  if (p->flags & ~(MOE_RD_FLAG_SKIP_IDENTITY_ROWS | MOE_RD_FLAG_TEST_GATE_STALL)) return MOE_RD_E_ENUM;
+  if (p->flags & ~(MOE_RD_FLAG_SKIP_IDENTITY_ROWS | MOE_RD_FLAG_TEST_GATE_STALL |
+                   MOE_RD_FLAG_SEPARATE_GATE_AND_ROUTING))
+    return MOE_RD_E_ENUM;
   if ((p->flags & MOE_RD_FLAG_SKIP_IDENTITY_ROWS) && p->rows_format != MOE_RD_ROWS_BF16)
     return MOE_RD_E_UNSUPPORTED;
   if (p->capacity < 0 || p->out_rows < 0 || p->out_rows > 0x7fffffff) return MOE_RD_E_SHAPE;
@@ -254,7 +256,8 @@ static int run_pipeline(const moe_rd_params* p, const moe_rd_buffers* b, void* w
   // before the first CTA has cleared the block)
   // Gate product and routing in one kernel where that pays (several token tiles per SM): its routing
   // warps add to the group counts while other CTAs are still starting, so the clear comes first.
-  const bool fused = p->T > 0 && fused_front_eligible(*p, *b, plan);
+  const bool fused = p->T > 0 && !(p->flags & MOE_RD_FLAG_SEPARATE_GATE_AND_ROUTING) &&
+                     fused_front_eligible(*p, *b, plan);
   const bool gate_clears = plan.gate == MOE_RD_GATE_UMMA && p->T > 0 && !fused &&
                            !(p->flags & MOE_RD_FLAG_TEST_GATE_STALL);
   if (!gate_clears) MOE_RD_CUDA(cudaMemsetAsync(ws + w.status, 0, w.zero_bytes, s));

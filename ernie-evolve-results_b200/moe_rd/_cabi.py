@@ -54,6 +54,7 @@ class GemmGroup(ctypes.Structure):
 
 FLAG_SKIP_IDENTITY_ROWS = 1
 FLAG_TEST_GATE_STALL = 2
+FLAG_SEPARATE_GATE_AND_ROUTING = 4
 
 
 class MoeRdError(RuntimeError):

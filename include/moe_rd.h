@@ -111,7 +111,11 @@ enum {
    * flight) and the limit is a few hundred polls, which makes that path run:
    * moe_rd_read_status then returns MOE_RD_E_DEVICE and the next call on the same
    * workspace works normally.  Ignored by the other gate implementations. */
-  MOE_RD_FLAG_TEST_GATE_STALL = 2
+  MOE_RD_FLAG_TEST_GATE_STALL = 2,
+  /* Keep the gate product and the routing in two kernels where the library would otherwise run them
+   * as one (several token tiles per SM, no split over K, at most 128 product columns).  Same results;
+   * for measuring the gate product alone. */
+  MOE_RD_FLAG_SEPARATE_GATE_AND_ROUTING = 4
 };
 
 /*

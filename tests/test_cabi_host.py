@@ -54,7 +54,7 @@ def test_workspace_bytes_and_validation():
            dict(n_groups=3), dict(E=64, K=8, n_groups=8, topk_groups=0, group_topk=2),
            dict(E=64, K=8, n_groups=16, topk_groups=1, group_topk=2), dict(score_fn=7),
            dict(rows_format=1, H=1000), dict(capacity=-1), dict(T=-1), dict(gate_impl=9), dict(w_dtype=3),
-           dict(flags=2), dict(flags=1, rows_format=1)]
+           dict(flags=8), dict(flags=1, rows_format=1)]
     for o in bad:
         with pytest.raises(_cabi.MoeRdError):
             _cabi.workspace_bytes(params(**o))
