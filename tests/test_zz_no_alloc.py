@@ -88,8 +88,10 @@ def _compare(name, T, H, warm=True):
     held_before = torch.cuda.memory_allocated(dev)
     _cabi.check(L.moe_rd_route_dispatch_noalloc(ctypes.byref(p), ctypes.byref(b2), stream))
     torch.cuda.synchronize()
-    if warm:  # the first call on a device may load the library's device image; later calls change nothing
-        assert torch.cuda.mem_get_info(dev)[0] == free_before
+    if warm:  # the first call on a device may load the library's device image; later calls take nothing
+        # (a device allocation comes in granules of 2 MiB or more; less free memory than before by a
+        # granule would be one)
+        assert torch.cuda.mem_get_info(dev)[0] > free_before - (1 << 20)
         assert torch.cuda.memory_allocated(dev) == held_before
     st = (ctypes.c_int32 * 8)()
     rc = L.moe_rd_read_status_noalloc(stream, st)
