@@ -74,6 +74,36 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return false;
 }
 
+// Non-blocking look at a barrier phase.  The answer is consumed later, so the
+// shared-memory round trip overlaps with the instructions issued in between.
+__device__ __forceinline__ uint32_t mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
+
+// Position in a ring of `stages` slots: the slot and the phase parity to wait
+// for.  The producer and the MMA issuer are single threads whose instruction
+// count per K block bounds the K loop (measured: with the slot, phase and
+// descriptors recomputed from the block index by division, the MMA thread alone
+// took 0.43 us per block where the tensor pipe needs 0.28), so everything that
+// can be stepped is stepped.
+struct Ring {
+  uint32_t s, ph;
+  __device__ __forceinline__ void next(uint32_t stages) {
+    if (++s == stages) {
+      s = 0;
+      ph ^= 1u;
+    }
+  }
+};
+
 // L2 policy for the loads of x: keep the lines if possible.  The row scatter reads x again right
 // after the routing front, and whatever part of x is still in L2 then does not come from HBM a
 // second time (measured on T=8192, H=7168: scatter 100.2 -> 97.2 us).
@@ -341,28 +371,30 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
       const uint64_t keep_x = policy_evict_last();
       int issued = 0;
+      Ring r{0u, 1u};
+      const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar), st0 = smem_u32(smem);
+      const int row = mt * a.mh * kBlockM, nbox = a.E / 64;
+      int kx = kb0 * kBlockK;
       for (int i = 0; i < nkb && !a.no_loads; ++i) {
-        const int s = i % a.stages;
-        const uint32_t use = (uint32_t)(i / a.stages);
-        if (!mbar_wait(smem_u32(empty_bar + s), (use & 1u) ^ 1u, abort_flag, a.spin_limit)) {
+        if (!mbar_wait(empty0 + 8u * r.s, r.ph, abort_flag, a.spin_limit)) {
           if (!*abort_flag) report(a.status, 101, mt, i);
           *abort_flag = 1;
           break;
         }
-        const uint32_t fb = smem_u32(full_bar + s);
+        const uint32_t fb = full0 + 8u * r.s;
         mbar_expect_tx(fb, stage_bytes);
-        unsigned char* st = smem + (size_t)s * stage_bytes;
-        for (int h = 0; h < a.mh; ++h)
-          tma_load_2d_keep(smem_u32(st + h * half_bytes), &map_x, (kb0 + i) * kBlockK,
-                           (mt * a.mh + h) * kBlockM, fb, keep_x);
+        const uint32_t st = st0 + r.s * stage_bytes;
+        tma_load_2d_keep(st, &map_x, kx, row, fb, keep_x);
+        if (a.mh == 2) tma_load_2d_keep(st + half_bytes, &map_x, kx, row + kBlockM, fb, keep_x);
         if (a.w_mn_major) {
           // one [64 h][64 e] box per block of 64 experts, 8 KB apart
-          for (int nb = 0; nb < a.E / 64; ++nb)
-            tma_load_2d(smem_u32(st + a_bytes + nb * 8192), &map_w, nb * 64, (kb0 + i) * kBlockK, fb);
+          for (int nb = 0; nb < nbox; ++nb) tma_load_2d(st + a_bytes + nb * 8192, &map_w, nb * 64, kx, fb);
         } else {
-          tma_load_2d(smem_u32(st + a_bytes), &map_w, (kb0 + i) * kBlockK, 0, fb);
+          tma_load_2d(st + a_bytes, &map_w, kx, 0, fb);
         }
         issued = i + 1;
+        kx += kBlockK;
+        r.next((uint32_t)a.stages);
       }
       if (*abort_flag) {
         // Do not leave the CTA while bulk copies into its shared memory are in
@@ -379,33 +411,41 @@ gate_umma_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constan
                              ((uint32_t)(kBlockM >> 4) << 24) |
                              (a.w_mn_major ? (1u << 16) : 0u);  // B major: 0 = K, 1 = MN
       bool ok = true;
+      Ring r{0u, 0u};
+      const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+      const uint64_t da_first = make_desc(smem_u32(smem));
+      const uint64_t db_first = a.w_mn_major ? make_desc_mn(smem_u32(smem + a_bytes), 8192u)
+                                             : make_desc(smem_u32(smem + a_bytes));
+      const uint64_t stage_units = (uint64_t)(stage_bytes >> 4);  // the address field counts 16 bytes
+      const uint64_t half_units = (uint64_t)(half_bytes >> 4);
+      // one UMMA_K step: 32 bytes inside the 128-byte swizzle row (K-major), two 1024-byte groups (MN-major)
+      const uint64_t kstep_a = (uint64_t)((kUmmaK * 2) >> 4);
+      const uint64_t kstep_b = a.w_mn_major ? (uint64_t)(2048 >> 4) : kstep_a;
+      uint32_t ready = 0;
       for (int i = 0; i < nkb && ok; ++i) {
-        const int s = i % a.stages;
-        const uint32_t use = (uint32_t)(i / a.stages);
-        if (!mbar_wait(smem_u32(full_bar + s), use & 1u, abort_flag, a.spin_limit)) {
+        if (!ready && !mbar_wait(full0 + 8u * r.s, r.ph, abort_flag, a.spin_limit)) {
           if (!*abort_flag) report(a.status, 102, mt, i);
           *abort_flag = 1;
           ok = false;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        unsigned char* st = smem + (size_t)s * stage_bytes;
-        const uint64_t da0 = make_desc(smem_u32(st));
-        const uint64_t da1 = make_desc(smem_u32(st + half_bytes));
-        const uint64_t db = a.w_mn_major ? make_desc_mn(smem_u32(st + a_bytes), 8192u)
-                                         : make_desc(smem_u32(st + a_bytes));
+        const uint64_t da0 = da_first + r.s * stage_units, da1 = da0 + half_units;
+        const uint64_t db = db_first + r.s * stage_units;
+        const uint32_t empty = empty0 + 8u * r.s;
+        r.next((uint32_t)a.stages);
+        // look at the next stage's barrier now; the answer is needed after these MMAs are issued
+        const uint32_t peek = mbar_test(full0 + 8u * r.s, r.ph);
 #pragma unroll
         for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-          // K-major: 16 elements = 32 bytes inside the 128-byte swizzle row;
-          // MN-major: 16 K-rows = two 1024-byte groups
-          const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);
-          const uint64_t step_b = a.w_mn_major ? (uint64_t)((k * 2048) >> 4) : step;
           const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-          umma_f16(tmem_base, da0 + step, db + step_b, idesc, acc);
+          umma_f16(tmem_base, da0 + (uint64_t)k * kstep_a, db + (uint64_t)k * kstep_b, idesc, acc);
           // the second 128-token half accumulates E columns further on
-          if (a.mh == 2) umma_f16(tmem_base + (uint32_t)a.E, da1 + step, db + step_b, idesc, acc);
+          if (a.mh == 2)
+            umma_f16(tmem_base + (uint32_t)a.E, da1 + (uint64_t)k * kstep_a, db + (uint64_t)k * kstep_b, idesc, acc);
         }
-        umma_commit(smem_u32(empty_bar + s));  // frees the stage once these MMAs have read it
+        umma_commit(empty);  // frees the stage once these MMAs have read it
+        ready = peek;
       }
       if (ok) umma_commit(smem_u32(accum_bar));
     }
@@ -488,29 +528,32 @@ gate_umma_pair_kernel(const __grid_constant__ CUtensorMap map_x,
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
       const uint64_t keep_x = policy_evict_last();
       int issued = 0;
+      Ring r{0u, 1u};
+      const uint32_t full_lead0 = map_to_cta(smem_u32(full_bar), 0u);  // the leader's full barriers
+      const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar), st0 = smem_u32(smem);
+      const int row = mt * kBlockM, nbox = a.E / 128;
+      int kx = kb0 * kBlockK;
       for (int i = 0; i < nkb && !a.no_loads; ++i) {
-        const int s = i % a.stages;
-        const uint32_t use = (uint32_t)(i / a.stages);
-        if (!mbar_wait(smem_u32(empty_bar + s), (use & 1u) ^ 1u, abort_flag, a.spin_limit)) {
+        if (!mbar_wait(empty0 + 8u * r.s, r.ph, abort_flag, a.spin_limit)) {
           if (!*abort_flag) report(a.status, 111, mt, i);
           *abort_flag = 1;
           break;
         }
         // the leader expects the bytes of both CTAs
-        if (rank == 0) mbar_expect_tx(smem_u32(full_bar + s), 2u * stage_bytes);
-        const uint32_t fb = map_to_cta(smem_u32(full_bar + s), 0u);
-        unsigned char* st = smem + (size_t)s * stage_bytes;
-        tma_load_2d_pair_keep(smem_u32(st), &map_x, (kb0 + i) * kBlockK, mt * kBlockM, fb, keep_x);
+        if (rank == 0) mbar_expect_tx(full0 + 8u * r.s, 2u * stage_bytes);
+        const uint32_t fb = full_lead0 + 8u * r.s;
+        const uint32_t st = st0 + r.s * stage_bytes;
+        tma_load_2d_pair_keep(st, &map_x, kx, row, fb, keep_x);
         if (a.w_mn_major) {
           // this CTA's E/128 boxes of [64 h][64 e], 8 KB apart
-          const int nbox = a.E / 128;
           for (int nb = 0; nb < nbox; ++nb)
-            tma_load_2d_pair(smem_u32(st + a_bytes + nb * 8192), &map_w, ((int)rank * nbox + nb) * 64,
-                             (kb0 + i) * kBlockK, fb);
+            tma_load_2d_pair(st + a_bytes + nb * 8192, &map_w, ((int)rank * nbox + nb) * 64, kx, fb);
         } else {
-          tma_load_2d_pair(smem_u32(st + a_bytes), &map_w, (kb0 + i) * kBlockK, (int)rank * (a.E / 2), fb);
+          tma_load_2d_pair(st + a_bytes, &map_w, kx, (int)rank * (a.E / 2), fb);
         }
         issued = i + 1;
+        kx += kBlockK;
+        r.next((uint32_t)a.stages);
       }
       if (*abort_flag && rank == 0) {
         // the leader's barriers see the loads of both CTAs: wait (bounded) for the
@@ -526,27 +569,35 @@ gate_umma_pair_kernel(const __grid_constant__ CUtensorMap map_x,
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.E >> 3) << 17) |
                              ((uint32_t)((2 * kBlockM) >> 4) << 24) | (a.w_mn_major ? (1u << 16) : 0u);
       bool ok = true;
+      Ring r{0u, 0u};
+      const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+      const uint64_t da0 = make_desc(smem_u32(smem));
+      const uint64_t db0 = a.w_mn_major ? make_desc_mn(smem_u32(smem + a_bytes), 8192u)
+                                        : make_desc(smem_u32(smem + a_bytes));
+      const uint64_t stage_units = (uint64_t)(stage_bytes >> 4);  // the address field counts 16 bytes
+      // one UMMA_K step: 32 bytes inside the 128-byte swizzle row (K-major), two 1024-byte groups (MN-major)
+      const uint64_t kstep_a = (uint64_t)((kUmmaK * 2) >> 4);
+      const uint64_t kstep_b = a.w_mn_major ? (uint64_t)(2048 >> 4) : kstep_a;
+      uint32_t ready = 0;
       for (int i = 0; i < nkb && ok; ++i) {
-        const int s = i % a.stages;
-        const uint32_t use = (uint32_t)(i / a.stages);
-        if (!mbar_wait(smem_u32(full_bar + s), use & 1u, abort_flag, a.spin_limit)) {
+        if (!ready && !mbar_wait(full0 + 8u * r.s, r.ph, abort_flag, a.spin_limit)) {
           if (!*abort_flag) report(a.status, 112, mt, i);
           *abort_flag = 1;
           ok = false;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        unsigned char* st = smem + (size_t)s * stage_bytes;
-        const uint64_t da = make_desc(smem_u32(st));
-        const uint64_t db = a.w_mn_major ? make_desc_mn(smem_u32(st + a_bytes), 8192u)
-                                         : make_desc(smem_u32(st + a_bytes));
+        const uint64_t da = da0 + r.s * stage_units, db = db0 + r.s * stage_units;
+        const uint32_t empty = empty0 + 8u * r.s;
+        r.next((uint32_t)a.stages);
+        // look at the next stage's barrier now; the answer is needed after these MMAs are issued
+        const uint32_t peek = mbar_test(full0 + 8u * r.s, r.ph);
 #pragma unroll
-        for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-          const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);
-          const uint64_t step_b = a.w_mn_major ? (uint64_t)((k * 2048) >> 4) : step;
-          umma_f16_pair(tmem_base, da + step, db + step_b, idesc, (i > 0 || k > 0) ? 1u : 0u);
-        }
-        umma_commit_pair(smem_u32(empty_bar + s));  // frees the stage in both CTAs
+        for (int k = 0; k < kBlockK / kUmmaK; ++k)
+          umma_f16_pair(tmem_base, da + (uint64_t)k * kstep_a, db + (uint64_t)k * kstep_b, idesc,
+                        (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit_pair(empty);  // frees the stage in both CTAs
+        ready = peek;
       }
       if (ok) umma_commit_pair(smem_u32(accum_bar));
     }
@@ -671,28 +722,31 @@ gate_route_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
       const uint64_t keep_x = policy_evict_last();
       int issued = 0;
       bool ok = true;
+      Ring r{0u, 1u};
+      const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar), st0 = smem_u32(smem);
+      const int nbox = a.N / 64;
       for (int it = 0; it < my_tiles && ok && !a.no_loads; ++it) {
         const int tile = (int)blockIdx.x + it * (int)gridDim.x;
+        int kx = 0;
         for (int kb = 0; kb < a.kblocks; ++kb) {
-          const int s = issued % a.stages;
-          const uint32_t use = (uint32_t)(issued / a.stages);
-          if (!mbar_wait(smem_u32(empty_bar + s), (use & 1u) ^ 1u, abort_flag, a.spin_limit)) {
+          if (!mbar_wait(empty0 + 8u * r.s, r.ph, abort_flag, a.spin_limit)) {
             if (!*abort_flag) report(a.status, 121, tile, kb);
             *abort_flag = 1;
             ok = false;
             break;
           }
-          const uint32_t fb = smem_u32(full_bar + s);
+          const uint32_t fb = full0 + 8u * r.s;
           mbar_expect_tx(fb, stage_bytes);
-          unsigned char* st = smem + (size_t)s * stage_bytes;
-          tma_load_2d_keep(smem_u32(st), &map_x, kb * kBlockK, tile * kBlockM, fb, keep_x);
+          const uint32_t st = st0 + r.s * stage_bytes;
+          tma_load_2d_keep(st, &map_x, kx, tile * kBlockM, fb, keep_x);
           if (a.w_mn_major) {
-            for (int nb = 0; nb < a.N / 64; ++nb)
-              tma_load_2d(smem_u32(st + a_bytes + nb * 8192), &map_w, nb * 64, kb * kBlockK, fb);
+            for (int nb = 0; nb < nbox; ++nb) tma_load_2d(st + a_bytes + nb * 8192, &map_w, nb * 64, kx, fb);
           } else {
-            tma_load_2d(smem_u32(st + a_bytes), &map_w, kb * kBlockK, 0, fb);
+            tma_load_2d(st + a_bytes, &map_w, kx, 0, fb);
           }
           ++issued;
+          kx += kBlockK;
+          r.next((uint32_t)a.stages);
         }
       }
       if (*abort_flag) {
@@ -706,8 +760,16 @@ gate_route_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
     if (lane == 0) {
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(a.N >> 3) << 17) |
                              ((uint32_t)(kBlockM >> 4) << 24) | (a.w_mn_major ? (1u << 16) : 0u);
-      int consumed = 0;
       bool ok = true;
+      Ring r{0u, 0u};
+      const uint32_t full0 = smem_u32(full_bar), empty0 = smem_u32(empty_bar);
+      const uint64_t da_first = make_desc(smem_u32(smem));
+      const uint64_t db_first = a.w_mn_major ? make_desc_mn(smem_u32(smem + a_bytes), 8192u)
+                                             : make_desc(smem_u32(smem + a_bytes));
+      const uint64_t stage_units = (uint64_t)(stage_bytes >> 4);  // the address field counts 16 bytes
+      const uint64_t kstep_a = (uint64_t)((kUmmaK * 2) >> 4);
+      const uint64_t kstep_b = a.w_mn_major ? (uint64_t)(2048 >> 4) : kstep_a;
+      uint32_t ready = 0;
       for (int it = 0; it < my_tiles && ok; ++it) {
         const int buf = it & 1;
         const int tile = (int)blockIdx.x + it * (int)gridDim.x;
@@ -718,28 +780,26 @@ gate_route_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_consta
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t acc_cols = tmem_base + (uint32_t)(buf * a.N);
         for (int kb = 0; kb < a.kblocks; ++kb) {
-          const int s = consumed % a.stages;
-          const uint32_t use = (uint32_t)(consumed / a.stages);
-          if (!mbar_wait(smem_u32(full_bar + s), use & 1u, abort_flag, a.spin_limit)) {
+          if (!ready && !mbar_wait(full0 + 8u * r.s, r.ph, abort_flag, a.spin_limit)) {
             if (!*abort_flag) report(a.status, 123, tile, kb);
             *abort_flag = 1;
             ok = false;
             break;
           }
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-          unsigned char* st = smem + (size_t)s * stage_bytes;
-          const uint64_t da = make_desc(smem_u32(st));
-          const uint64_t db = a.w_mn_major ? make_desc_mn(smem_u32(st + a_bytes), 8192u)
-                                           : make_desc(smem_u32(st + a_bytes));
+          const uint64_t da = da_first + r.s * stage_units, db = db_first + r.s * stage_units;
+          const uint32_t empty = empty0 + 8u * r.s;
+          r.next((uint32_t)a.stages);
+          // look at the next stage's barrier now; the answer is needed after these MMAs are issued
+          const uint32_t peek = mbar_test(full0 + 8u * r.s, r.ph);
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            const uint64_t step = (uint64_t)((k * kUmmaK * 2) >> 4);
-            const uint64_t step_b = a.w_mn_major ? (uint64_t)((k * 2048) >> 4) : step;
-            umma_f16(tmem_base + (uint32_t)(buf * a.N), da + step, db + step_b, idesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
-          umma_commit(smem_u32(empty_bar + s));
-          ++consumed;
+          for (int k = 0; k < kBlockK / kUmmaK; ++k)
+            umma_f16(acc_cols, da + (uint64_t)k * kstep_a, db + (uint64_t)k * kstep_b, idesc,
+                     (kb > 0 || k > 0) ? 1u : 0u);
+          umma_commit(empty);
+          ready = peek;
         }
         if (ok) umma_commit(smem_u32(tmem_full + buf));
       }
