@@ -605,6 +605,51 @@ def run_combine(args):
         "gpu_launches": args.steps}), flush=True)
 
 
+def run_combine_add(args):
+    """`--op combine_add`: the residual (accumulating) combine on the workload's shapes (one GPU) with every
+    row live, i.e. its worst case; same timing rules.  Bytes: every row of y once, row metadata, and the rows
+    of `out` the reductions land on, once each way (they are resolved in L2 while the K rows of a token
+    arrive)."""
+    import torch
+    import moe_rd
+    from moe_rd import workloads
+    spec = workloads.SPECS[args.workload]
+    T, H, K = spec["T"], spec["H"], spec["K"]
+    dev = torch.device("cuda", 0)
+    g = torch.Generator(device="cpu").manual_seed(7)
+    R = T * K
+    y = torch.randn(R, H, generator=g, dtype=torch.float32).to(torch.bfloat16).to(dev)
+    out = torch.randn(T, H, generator=g, dtype=torch.float32).to(torch.bfloat16).to(dev)
+    tok = (torch.randperm(R, generator=g) % T).to(torch.int32).to(dev)
+    w = torch.rand(R, generator=g).to(dev)
+    n = torch.tensor([R], dtype=torch.int32, device=dev)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    for _ in range(max(args.warmup, 3)):
+        moe_rd.combine_add_rows(y, tok, w, n, out)
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    torch.cuda.synchronize()
+    for s_, e_ in ev:
+        flush.zero_()
+        s_.record()
+        moe_rd.combine_add_rows(y, tok, w, n, out)
+        e_.record()
+    torch.cuda.synchronize()
+    ms = sum(s_.elapsed_time(e_) for s_, e_ in ev) / args.steps
+    nbytes = R * H * 2 + 2 * T * H * 2 + R * 8
+    peak, kind = measured_hbm_peak()
+    gbs = nbytes / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "metric": "combined_tokens_per_s", "value": T / (ms * 1e-3), "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload + " residual combine, all rows live", "tokens": T, "hidden": H,
+                   "top_k": K, "l2": "flushed by a 256 MiB device write between steps"},
+        "roofline": {"bound": "hbm", "kernel": "combine_add_rows_kernel", "achieved": gbs, "peak": peak,
+                     "unit": "GB/s", "frac": gbs / peak, "peak_kind": f"{kind} HBM copy bandwidth", "traffic": None,
+                     "bytes_per_launch": nbytes, "kernel_ms": ms},
+        "gpu_launches": args.steps}), flush=True)
+
+
 def run_combine_ep(args, rank, world, local_rank):
     """`--op combine` at N > 1: the expert-parallel combine (every rank pulls its pairs' expert outputs from
     the owning ranks over NVLink inside the combine kernel).  Routing and the dispatch run once, untimed, to
@@ -682,7 +727,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true",
                     help="skip the other_workloads / gate_vs_cublas legs of the N = 1 line")
     ap.add_argument("--scatter", default="auto", choices=["auto", "simt", "bulk"])
-    ap.add_argument("--op", default="route_dispatch", choices=["route_dispatch", "combine"])
+    ap.add_argument("--op", default="route_dispatch", choices=["route_dispatch", "combine", "combine_add"])
     ap.add_argument("--ep-layout", default=None, choices=["packed", "separate"],
                     help="fused exchange, fp8 rows: scales after each row (one copy per pair) or in a buffer of their own")
     ap.add_argument("--ep", default="fused", choices=["fused", "nccl"],
@@ -691,6 +736,10 @@ def main():
     rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if world == 1 and args.gpus > 1:
         raise SystemExit("launch with torchrun for --gpus > 1 (one process per GPU)")
+    if args.op == "combine_add":
+        if rank == 0:
+            run_combine_add(args)
+        return
     if args.op == "combine":
         if world > 1:
             run_combine_ep(args, rank, world, local_rank)

@@ -205,8 +205,92 @@ int launch_combine(CombineArgs& a, int64_t T, int32_t H, int32_t K, void* stream
   return e == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
 }
 
+// ---------------------------------------------------------------------------
+// Residual (accumulating) combine over expert-major rows:
+//   out[row_token[p], :] += bf16(row_weight[p] * y[p, :])   for p < *n_rows
+// The form the reference uses when most expert outputs were already reduced
+// into `out` by a GEMM epilogue and only the rows of the remaining experts are
+// left to fold in (raddleft_kernel, kernel.cu:2451-2486): it must add, not
+// store, and the number of live rows is a device-side value, so nothing is
+// read back.  The product is rounded to bf16 and added by an element-wise bf16
+// reduction without return value (kernel.cu:2446-2449); here one 16-byte
+// vector reduction (red.global.add.noftz.v4.bf16x2) per lane where the
+// reference issues four 4-byte ones.  Adds to one element from different rows
+// arrive in no fixed order, each rounding to bf16: results are exact when every
+// token receives at most one row and order-dependent in the last bits otherwise
+// (as in the reference).  Work units (a row x 32 vectors) are dealt to warps
+// grid-stride.
+// ---------------------------------------------------------------------------
+struct AddRowsArgs {
+  const uint4* y;
+  const int32_t* row_token;
+  const float* row_weight;
+  const int32_t* n_rows;  // device value
+  uint4* out;
+  int64_t max_rows;
+  int nvec;
+};
+
+__device__ __forceinline__ void red_add_bf16x8(void* p, const uint32_t (&v)[4]) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v[0]), "r"(v[1]),
+               "r"(v[2]), "r"(v[3])
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kCombineThreads) combine_add_rows_kernel(const AddRowsArgs a) {
+  pdl_sync();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * kCombineWarps + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * kCombineWarps;
+  int64_t n = __ldg(a.n_rows);
+  n = n < 0 ? 0 : (n > a.max_rows ? a.max_rows : n);
+  const int chunks = (a.nvec + 31) / 32;
+  for (int64_t u = warp; u < n * chunks; u += nwarps) {
+    const int64_t p = u / chunks;
+    const int v = (int)(u - p * chunks) * 32 + lane;
+    const int t = __ldg(a.row_token + p);
+    if (v >= a.nvec || t < 0) continue;
+    const float w = __ldg(a.row_weight + p);
+    const uint4 yv = __ldcs(a.y + (size_t)p * a.nvec + v);
+    const uint32_t in[4] = {yv.x, yv.y, yv.z, yv.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      o[j] = pack_bf16x2(__fmul_rn(w, __uint_as_float(in[j] << 16)),
+                         __fmul_rn(w, __uint_as_float(in[j] & 0xffff0000u)));
+    red_add_bf16x8(a.out + (size_t)t * a.nvec + v, o);
+  }
+}
+
 }  // namespace
 }  // namespace moe_rd
+
+extern "C" int moe_rd_combine_add_rows(int32_t H, int64_t max_rows, const void* y, const int32_t* row_token,
+                                       const float* row_weight, const int32_t* n_rows, void* out,
+                                       void* stream) {
+  if (H < 8 || H % 8 != 0 || max_rows < 0 || max_rows > ((int64_t)1 << 31) - 1) return MOE_RD_E_SHAPE;
+  if (max_rows == 0) return MOE_RD_OK;
+  if (y == nullptr || row_token == nullptr || row_weight == nullptr || n_rows == nullptr || out == nullptr)
+    return MOE_RD_E_NULL;
+  if ((reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(out)) & 15) return MOE_RD_E_ALIGN;
+  AddRowsArgs a = {};
+  a.y = static_cast<const uint4*>(y);
+  a.row_token = row_token;
+  a.row_weight = row_weight;
+  a.n_rows = n_rows;
+  a.out = static_cast<uint4*>(out);
+  a.max_rows = max_rows;
+  a.nvec = H / 8;
+  const int64_t units = max_rows * ((a.nvec + 31) / 32);
+  const int64_t want = (units + kCombineWarps - 1) / kCombineWarps;
+  const int64_t cap = (int64_t)device_sms() * kCombineBlocksPerSm;
+  const dim3 grid((unsigned)(want < cap ? want : cap));
+  const cudaError_t e =
+      launch_pdl(combine_add_rows_kernel, grid, dim3(kCombineThreads), 0, static_cast<cudaStream_t>(stream), a);
+  count_launch();
+  if (e != cudaSuccess) set_last_cuda_error(e);
+  return e == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
+}
 
 extern "C" int moe_rd_combine(int64_t T, int32_t H, int32_t K, const void* y,
                               const int32_t* inverse_perm, const float* combine_weights,

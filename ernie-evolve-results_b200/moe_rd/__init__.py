@@ -21,7 +21,7 @@ import torch
 from . import _cabi
 from ._cabi import MoeRdError  # noqa: F401
 
-__all__ = ["route_dispatch", "combine", "gemm_plan", "expert_stats", "RouteDispatchResult", "ExpertStats",
+__all__ = ["route_dispatch", "combine", "combine_add_rows", "gemm_plan", "expert_stats", "RouteDispatchResult", "ExpertStats",
            "MoeRdError", "capacity_from_factor"]
 
 
@@ -241,6 +241,42 @@ def combine(y: torch.Tensor, inverse_perm: torch.Tensor, combine_weights: torch.
     applied: ``y`` holds the expert outputs in expert-major row order.  Mirrors
     the reference's combine_kernel (kernel.cu:2365-2428)."""
     return torch.ops.moe_rd.combine(y, inverse_perm, combine_weights, shared)
+
+
+def _combine_add_rows_impl(y, row_token, row_weight, n_rows, out):
+    if not y.is_cuda:
+        raise RuntimeError("moe_rd.combine_add_rows has no CPU path")
+    if (y.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or row_token.dtype != torch.int32
+            or row_weight.dtype != torch.float32 or n_rows.dtype != torch.int32):
+        raise TypeError("combine_add_rows expects y/out bf16, row_token/n_rows int32, row_weight float32")
+    if not (y.is_contiguous() and out.is_contiguous() and row_token.is_contiguous() and row_weight.is_contiguous()):
+        raise ValueError("combine_add_rows updates out in place and takes contiguous tensors")
+    H = y.shape[-1]
+    max_rows = min(y.shape[0], row_token.numel(), row_weight.numel())
+    if out.shape[-1] != H or n_rows.numel() < 1:
+        raise ValueError("combine_add_rows: out must be [T,H] like y's rows, n_rows a device int32 scalar")
+    with torch.cuda.device(y.device):
+        stream = ctypes.c_void_p(torch.cuda.current_stream(y.device).cuda_stream)
+        _cabi.check(_cabi.lib().moe_rd_combine_add_rows(H, max_rows, _ptr(y), _ptr(row_token), _ptr(row_weight),
+                                                        _ptr(n_rows), _ptr(out), stream))
+
+
+_torch_lib.define("combine_add_rows(Tensor y, Tensor row_token, Tensor row_weight, Tensor n_rows, "
+                  "Tensor(a!) out) -> ()")
+_torch_lib.impl("combine_add_rows", _combine_add_rows_impl, "CUDA")
+
+
+def combine_add_rows(y: torch.Tensor, row_token: torch.Tensor, row_weight: torch.Tensor, n_rows: torch.Tensor,
+                     out: torch.Tensor) -> torch.Tensor:
+    """out[row_token[p]] += bf16(row_weight[p] * y[p]) for p < n_rows, in place; returns ``out``.
+
+    The residual combine of a pipeline whose expert GEMM already reduced most outputs into ``out``
+    (the reference's raddleft_kernel, kernel.cu:2451-2486).  ``row_token`` / ``row_weight`` are what
+    ``route_dispatch(..., return_row_meta=True)`` returns; ``n_rows`` is a DEVICE int32 tensor (for
+    example ``offsets[-1:]``), so the number of live rows is never read back.  The adds are bf16
+    reductions in no fixed order: bit-exact when a token receives at most one row."""
+    torch.ops.moe_rd.combine_add_rows(y, row_token, row_weight, n_rows, out)
+    return out
 
 
 def gemm_plan(offsets: torch.Tensor, rows: torch.Tensor, expert_weights: torch.Tensor, out: torch.Tensor,

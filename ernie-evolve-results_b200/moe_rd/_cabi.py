@@ -20,6 +20,7 @@ SCATTER_IMPL = {"auto": 0, "simt": 1, "bulk": 2, "none": 3}
 EXPORTS = (
     "moe_rd_workspace_bytes", "moe_rd_route_dispatch", "moe_rd_route_dispatch_noalloc",
     "moe_rd_route_dispatch_timed", "moe_rd_read_status", "moe_rd_ep_unpack", "moe_rd_ep_plan", "moe_rd_combine",
+    "moe_rd_combine_add_rows",
     "moe_rd_ep_scatter", "moe_rd_ep_combine", "moe_rd_read_status_noalloc", "moe_rd_gemm_plan", "moe_rd_expert_stats",
     "moe_rd_launch_count", "moe_rd_strerror", "moe_rd_last_cuda_error", "moe_rd_version",
 )
@@ -100,6 +101,9 @@ def lib() -> ctypes.CDLL:
         L.moe_rd_combine.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p,
                                      ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         L.moe_rd_combine.restype = ctypes.c_int
+        L.moe_rd_combine_add_rows.argtypes = [ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p,
+                                              ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+        L.moe_rd_combine_add_rows.restype = ctypes.c_int
         L.moe_rd_read_status_noalloc.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]
         L.moe_rd_read_status_noalloc.restype = ctypes.c_int
         L.moe_rd_ep_combine.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32, ctypes.c_int32,

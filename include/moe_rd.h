@@ -259,6 +259,23 @@ int moe_rd_combine(int64_t T, int32_t H, int32_t K, const void* y, const int32_t
                    const float* combine_weights, const void* shared, void* out, void* stream);
 
 /*
+ * Residual (accumulating) combine over expert-major rows, the reference's
+ * raddleft_kernel (kernel.cu:2451-2486), for a pipeline in which most expert
+ * outputs were already reduced into `out` and only the first *n_rows rows of y
+ * are left to fold in:
+ *   out[row_token[p],:] += bf16(row_weight[p] * y[p,:])     for p < min(*n_rows, max_rows)
+ * y [max_rows,H] bf16; row_token / row_weight as moe_rd_buffers returns them
+ * (rows with row_token < 0 are skipped); n_rows is a DEVICE int32 (for example
+ * &offsets[E]), so the count is never read back; out [T,H] bf16 is updated in
+ * place.  The product is rounded to bf16 and added with an element-wise bf16
+ * reduction (red.global.add.noftz, kernel.cu:2446-2449): exact when every token
+ * receives at most one row; with several rows per token the adds reach an
+ * element in no fixed order and the last bits depend on it, as in the reference.
+ */
+int moe_rd_combine_add_rows(int32_t H, int64_t max_rows, const void* y, const int32_t* row_token,
+                            const float* row_weight, const int32_t* n_rows, void* out, void* stream);
+
+/*
  * Same work as moe_rd_route_dispatch, but with a CUDA event recorded on
  * `stream` between the stages; synchronises the stream and returns the device
  * time of each stage in milliseconds: stage_ms[0] gate product, [1] scoring /

@@ -69,6 +69,8 @@ def lib() -> ctypes.CDLL:
         L.moe_oracle_e4m3_to_f32.restype = f32
         L.moe_oracle_combine.argtypes = [vp, vp, vp, vp, i64, i32, i32, vp]
         L.moe_oracle_combine.restype = None
+        L.moe_oracle_combine_add_rows.argtypes = [vp, vp, vp, i64, i32, vp]
+        L.moe_oracle_combine_add_rows.restype = None
         L.moe_oracle_max_threads.restype = i32
         L.moe_oracle_set_threads.argtypes = [i32]
         _lib = L
@@ -207,6 +209,17 @@ def combine(y_u16, inverse_perm, weights, shared_u16=None):
     H = y.shape[1]
     out = np.empty((T, H), np.uint16)
     lib().moe_oracle_combine(_p(y), _p(inv), _p(w), _p(sh), T, K, H, _p(out))
+    return out
+
+
+def combine_add_rows(y_u16, row_token, row_weight, n_rows, out_u16):
+    """out[row_token[p]] += bf16(row_weight[p] * y[p]) for p < n_rows, rows in ascending order
+    (bf16 bits; returns the updated copy of ``out_u16``)."""
+    y = _c(y_u16, np.uint16)
+    tok = _c(row_token, np.int32)
+    wt = _c(row_weight, np.float32)
+    out = np.array(out_u16, dtype=np.uint16, order="C", copy=True)
+    lib().moe_oracle_combine_add_rows(_p(y), _p(tok), _p(wt), int(n_rows), y.shape[1], _p(out))
     return out
 
 

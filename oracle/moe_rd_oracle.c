@@ -420,6 +420,46 @@ void moe_oracle_combine(const uint16_t* y, const int32_t* inverse_perm, const fl
   }
 }
 
+/* ------------------------------------------------------------------------
+ * Residual (accumulating) combine over expert-major rows, raddleft_kernel
+ * (kernel.cu:2451-2486): out[tok[p],:] += bf16(w[p] * y[p,:]) for p < n_rows,
+ * rows taken in ascending p.  The product is an fp32 multiply rounded to bf16
+ * (kernel.cu:2466-2467); the add is one bf16 addition with a single rounding
+ * (red.global.add.noftz.bf16x2, kernel.cu:2446-2449), computed here in double,
+ * where the sum of two bf16 values cannot be rounded twice to a different bf16.
+ * The GPU adds rows of one token in no fixed order: this is the result for ONE
+ * order, exact for the GPU only when a token has at most one row.
+ * ---------------------------------------------------------------------- */
+static inline uint16_t f64_to_bf16_rne(double d) {
+  /* double -> fp32 with round-to-odd (truncate toward zero, inexact sets the last bit), then the
+   * usual round-to-nearest-even to bf16: with 16 spare bits the two steps equal one rounding */
+  float f = (float)d;
+  if ((double)f != d && f == f) {
+    uint32_t u;
+    const double fa = f < 0 ? -(double)f : (double)f, da = d < 0 ? -d : d;
+    memcpy(&u, &f, 4);
+    if (fa > da) u -= 1u; /* one step toward zero (sign-magnitude encoding) */
+    u |= 1u;
+    memcpy(&f, &u, 4);
+  }
+  return f32_to_bf16_rne(f);
+}
+
+void moe_oracle_combine_add_rows(const uint16_t* y, const int32_t* row_token, const float* row_weight,
+                                 int64_t n_rows, int H, uint16_t* out) {
+  for (int64_t p = 0; p < n_rows; ++p) {
+    const int32_t t = row_token[p];
+    if (t < 0) continue;
+    const float w = row_weight[p];
+    for (int h = 0; h < H; ++h) {
+      const float prod = w * bf16_to_f32(y[(size_t)p * H + h]);
+      const double term = (double)bf16_to_f32(f32_to_bf16_rne(prod));
+      uint16_t* o = out + (size_t)t * H + h;
+      *o = f64_to_bf16_rne((double)bf16_to_f32(*o) + term);
+    }
+  }
+}
+
 int moe_oracle_max_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -73,6 +73,22 @@ def test_route_dispatch_rejects_null_buffers_before_any_cuda_call():
     assert L.moe_rd_route_dispatch(ctypes.byref(p), None, None, 0, None) == -1
 
 
+def test_residual_combine_validates_before_any_cuda_call():
+    L = _cabi.lib()
+    buf = (ctypes.c_char * 64)()
+    a = ctypes.addressof(buf)
+    a16 = (a + 15) & ~15
+    ok = (ctypes.c_void_p(a16),) * 5
+    assert L.moe_rd_combine_add_rows(7, 4, *ok, None) == L.moe_rd_combine_add_rows(12, 4, *ok, None) != 0   # H % 8
+    assert L.moe_rd_combine_add_rows(64, -1, *ok, None) != 0
+    assert L.moe_rd_combine_add_rows(64, 0, None, None, None, None, None, None) == 0                       # nothing to do
+    assert L.moe_rd_combine_add_rows(64, 4, None, *ok[1:], None) == -1                                      # null
+    assert L.moe_rd_combine_add_rows(64, 4, ctypes.c_void_p(a16 + 2), *ok[1:], None) not in (0, -1)         # alignment
+    with pytest.raises((RuntimeError, NotImplementedError)):
+        z = torch.zeros(4, 64, dtype=torch.bfloat16)
+        moe_rd.combine_add_rows(z, torch.zeros(4, dtype=torch.int32), torch.zeros(4), torch.zeros(1, dtype=torch.int32), z)
+
+
 def test_no_cpu_path():
     x = torch.zeros(4, 64, dtype=torch.bfloat16)
     w = torch.zeros(64, 8, dtype=torch.bfloat16)

@@ -322,6 +322,42 @@ def test_combine_matches_numpy_restatement():
         np.testing.assert_array_equal(got, _util.bf16_bits(ref))
 
 
+def _bf16_nearest_even(s):
+    """float64 -> bf16 bits, one rounding, by comparing with the two neighbouring bf16 values."""
+    f = s.astype(np.float32)
+    lo_bits = f.view(np.uint32) & np.uint32(0xffff0000)          # toward zero
+    hi_bits = lo_bits + np.uint32(0x10000)                        # away from zero
+    lo = lo_bits.view(np.float32).astype(np.float64)
+    hi = hi_bits.view(np.float32).astype(np.float64)
+    dl, dh = np.abs(s - lo), np.abs(hi - s)
+    up = (dh < dl) | ((dh == dl) & (((lo_bits >> 16) & 1) == 1))
+    return np.where(up, hi_bits >> 16, lo_bits >> 16).astype(np.uint16)
+
+
+def test_residual_combine_matches_numpy_restatement():
+    g = torch.Generator().manual_seed(22)
+    T, H, R, live = 50, 72, 120, 97
+    y = torch.randn(R, H, generator=g).to(torch.bfloat16)
+    out0 = (torch.randn(T, H, generator=g) * 3).to(torch.bfloat16)
+    rng = np.random.default_rng(4)
+    tok = rng.integers(-1, T, size=R).astype(np.int32)              # several rows per token, some without one
+    w = (rng.random(R) * 2 - 0.5).astype(np.float32)
+    got = cpu_oracle.combine_add_rows(_util.bf16_bits(y), tok, w, live, _util.bf16_bits(out0))
+    ref = out0.float().numpy().astype(np.float64)
+    yf = y.float().numpy()
+    for p in range(live):                                           # ascending rows, one bf16 add each
+        if tok[p] < 0:
+            continue
+        term = torch.from_numpy(w[p] * yf[p]).to(torch.bfloat16).float().numpy().astype(np.float64)
+        bits = _bf16_nearest_even(ref[tok[p]] + term)
+        ref[tok[p]] = (bits.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    np.testing.assert_array_equal(got, _bf16_nearest_even(ref))
+    # rows past the live count and tokens nobody points at are untouched
+    hit = np.zeros(T, bool)
+    hit[tok[:live][tok[:live] >= 0]] = True
+    np.testing.assert_array_equal(got[~hit], _util.bf16_bits(out0)[~hit])
+
+
 def test_row_meta_expert_stats_and_plan_restatements():
     inv = np.array([[2, 0], [-1, 1], [3, 4]], dtype=np.int32)
     w = np.array([[0.5, 0.25], [0.125, 1.0], [2.0, 4.0]], dtype=np.float32)
