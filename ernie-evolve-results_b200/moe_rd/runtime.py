@@ -80,6 +80,21 @@ class Session:
             self.ws_bytes, stream))
         return self.result()
 
+    def capture(self, x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> "torch.cuda.CUDAGraph":
+        """Record one pass into a CUDA graph and return it; ``graph.replay()`` repeats the pass on the same
+        input and output buffers (refill ``x`` / ``w`` / ``bias`` in place between replays).  The call only
+        enqueues kernels and one memset on the given stream - no allocation, no host synchronisation, the
+        tensor maps are kernel parameters - so it captures as it is, programmatic launch dependencies between
+        its kernels included; a replay pays one submission instead of four or five launches, which is what
+        matters for the launch-bound small shapes."""
+        self.run(x, w, bias)                    # one-time function attributes are set outside the capture
+        torch.cuda.synchronize(self.device)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self.run(x, w, bias)
+        self._captured_inputs = (x, w, bias)    # the graph holds their addresses
+        return graph
+
     def run_timed(self, x, w, bias=None):
         """One pass with per-stage device times in ms: (gate, route, scan, positions, scatter). Synchronises."""
         self._check_inputs(x, w)

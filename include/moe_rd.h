@@ -152,6 +152,9 @@ int moe_rd_workspace_bytes(const moe_rd_params* p, size_t* bytes);
  * topk_kernel, offsets_kernel, dispatch_kernel, gather_kernel), enqueued on
  * `stream` (a cudaStream_t) with no host synchronisation.  `workspace` is
  * device memory, 256-byte aligned, of at least moe_rd_workspace_bytes bytes.
+ * Nothing is allocated and nothing read back, so the call may be recorded into a
+ * CUDA graph (stream capture) after one plain call has set the per-device
+ * function attributes; the graph holds the buffer addresses of the recorded call.
  */
 int moe_rd_route_dispatch(const moe_rd_params* p, const moe_rd_buffers* b,
                           void* workspace, size_t workspace_bytes, void* stream);
