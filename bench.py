@@ -440,6 +440,19 @@ def run_ours(args, rank, world, local_rank):
     if world > 1:
         dist.all_reduce(e2e_ms, op=dist.ReduceOp.MAX)
     e2e_value = world * T * e2e_steps / (float(e2e_ms.item()) / 1e3)
+    e2e_extra = {}
+    if world == 1:
+        # The same loop as a serving process would run it: copies on streams of their own and two sets of
+        # buffers, so that step i's read-back, step i+1's pass and step i+2's upload overlap (PCIe carries
+        # both directions at once).  Every step still uploads its inputs from pinned memory, runs the call
+        # through the public Session with a cold L2, and reads every output back; only the waiting is gone.
+        e2e_extra = {"serial_value": e2e_value,
+                     "note": "value: uploads, calls and read-backs of consecutive steps overlapped on three "
+                             "streams with two sets of buffers; serial_value: one step at a time on one stream"}
+        e2e_value = T * e2e_steps / (pipelined_e2e_ms(sess, Session(T, H, E, K, device=dev, w_dtype=w.dtype,
+                                                                    scatter_impl=args.scatter,
+                                                                    **session_kwargs(kw)),
+                                                      x_host, w, bias, flush, e2e_steps) / 1e3)
 
     sweep = None
     if world == 1 and not args.no_sweep:
@@ -455,8 +468,8 @@ def run_ours(args, rank, world, local_rank):
             "vs_baseline": None, "dtype": "fp32", "data": "synthetic",
             "config": workload_config(name, spec, world),
             "roofline": roofline,
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                    "steps": e2e_steps},
+            "e2e": dict({"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                         "steps": e2e_steps}, **e2e_extra),
             "gpu_launches": int(launches),
             "nvlink": nvlink,
             "clocks": clocks,
@@ -473,6 +486,61 @@ def run_ours(args, rank, world, local_rank):
         dist.destroy_process_group()
     if line is not None:
         print(json.dumps(line), flush=True)
+
+
+def pipelined_e2e_ms(sess_a, sess_b, x_host, w, bias, flush, steps):
+    """Device time of `steps` end-to-end steps (after two untimed ones): upload of x from pinned memory ->
+    Session.run -> read-back of every output into pinned memory, with the three phases of consecutive steps
+    on three streams and two sets of device and host buffers."""
+    import torch
+    dev = sess_a.device
+    sessions = (sess_a, sess_b)
+    x_in = [torch.empty(x_host.shape, dtype=x_host.dtype, device=dev) for _ in range(2)]
+
+    def outputs(sess):
+        return [t for t in (sess.permuted, sess.scales, sess.offsets, sess.inverse_perm, sess.combine_weights)
+                if t is not None]
+
+    host = [[torch.empty(t.shape, dtype=t.dtype).pin_memory() for t in outputs(sv)] for sv in sessions]
+    up, run, down = torch.cuda.Stream(dev), torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    uploaded = [torch.cuda.Event() for _ in range(2)]
+    computed = [torch.cuda.Event() for _ in range(2)]
+    read_back = [torch.cuda.Event() for _ in range(2)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    torch.cuda.synchronize(dev)
+
+    def one(i):
+        k = i & 1
+        with torch.cuda.stream(up):
+            if i >= 2:
+                up.wait_event(computed[k])        # the pass two steps ago has read this input buffer
+            x_in[k].copy_(x_host, non_blocking=True)
+            uploaded[k].record(up)
+        with torch.cuda.stream(run):
+            run.wait_event(uploaded[k])
+            if i >= 2:
+                run.wait_event(read_back[k])      # its outputs have been read back
+            flush.zero_()
+            sessions[k].run(x_in[k], w, bias)
+            computed[k].record(run)
+        with torch.cuda.stream(down):
+            down.wait_event(computed[k])
+            for h, d in zip(host[k], outputs(sessions[k])):
+                h.copy_(d, non_blocking=True)
+            read_back[k].record(down)
+
+    for i in range(2):
+        one(i)
+    torch.cuda.synchronize(dev)
+    t0.record(up)
+    for i in range(2, 2 + steps):
+        one(i)
+    with torch.cuda.stream(down):
+        t1.record(down)
+    torch.cuda.synchronize(dev)
+    for sv in sessions:
+        sv.status()
+    return t0.elapsed_time(t1)
 
 
 def graph_replay_ms(sess, x, w, bias, flush, steps):
