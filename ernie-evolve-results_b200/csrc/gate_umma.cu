@@ -315,7 +315,9 @@ __device__ __forceinline__ void epilogue_rows(const UmmaArgs& a, unsigned char* 
         if (row < a.T)
           bulk_store_row(a.partial + ((size_t)ks * a.T + row) * a.E, smem_u32(my_row), (uint32_t)a.E * 4u);
       }
-      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+      // the rows must have left shared memory before the CTA may go; their arrival in global
+      // memory is ordered before the next kernel by the end of this grid
+      asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
 }
 
