@@ -252,7 +252,7 @@ def run_ours(args, rank, world, local_rank):
         from moe_rd.ep import ExpertParallel, ExpertParallelFused
         ep = (ExpertParallelFused(sess, dist.group.WORLD,
                                   bulk={"auto": None, "bulk": True, "simt": False}[args.scatter],
-                                  layout=args.ep_layout) if fused
+                                  layout=args.ep_layout, send_once=False if args.ep_every_pair else None) if fused
               else ExpertParallel(sess, dist.group.WORLD))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
@@ -355,16 +355,27 @@ def run_ours(args, rank, world, local_rank):
         ex_ms = statistics.mean(s_.elapsed_time(e_) for s_, e_ in evx)
         offs = sess.offsets.cpu()
         epr = E // world
-        egress = float((int(offs[E]) - int(offs[(rank + 1) * epr] - offs[rank * epr])) * row_bytes)
-        # rows this rank RECEIVES from the other ranks (routing can load the owners unevenly)
-        kept_me = (sess.offsets[1:] - sess.offsets[:-1]).to(torch.int64)
-        kept_all = [torch.empty_like(kept_me) for _ in range(world)]
-        dist.all_gather(kept_all, kept_me)
-        mine = slice(rank * epr, (rank + 1) * epr)
-        ingress = float(sum(int(k[mine].sum()) for r_, k in enumerate(kept_all) if r_ != rank) * row_bytes)
-        red = torch.tensor([ex_ms, egress, op_ms, ingress], dtype=torch.float64, device=dev)
+        send_once = bool(getattr(ep, "send_once", False))
+        # bytes this rank sends to every rank d: one row per kept pair, or, with the send-once exchange, one row
+        # per (token, rank) that has a kept pair there plus a 4-byte mark for each further pair
+        owner = (sess.expert_ids // epr).to(torch.int64)
+        valid = sess.inverse_perm >= 0
+        sent = torch.zeros(world, dtype=torch.float64, device=dev)
+        for d in range(world):
+            per_token = ((owner == d) & valid).sum(dim=1)
+            if send_once:
+                sent[d] = float((per_token > 0).sum()) * row_bytes + float((per_token - 1).clamp_min(0).sum()) * 4
+            else:
+                sent[d] = float(per_token.sum()) * row_bytes
+        sent_all = [torch.empty_like(sent) for _ in range(world)]
+        dist.all_gather(sent_all, sent)
+        egress = float(sum(float(sent[d]) for d in range(world) if d != rank))
+        # bytes this rank RECEIVES from the other ranks (routing can load the owners unevenly)
+        ingress = float(sum(float(v[rank]) for r_, v in enumerate(sent_all) if r_ != rank))
+        all_pairs_egress = float((int(offs[E]) - int(offs[(rank + 1) * epr] - offs[rank * epr])) * row_bytes)
+        red = torch.tensor([ex_ms, egress, op_ms, ingress, all_pairs_egress], dtype=torch.float64, device=dev)
         dist.all_reduce(red, op=dist.ReduceOp.MAX)
-        ex_ms, egress, step_ms, ingress_max = (float(v) for v in red)
+        ex_ms, egress, step_ms, ingress_max, all_pairs_egress = (float(v) for v in red)
         mean = torch.tensor([ingress], dtype=torch.float64, device=dev)
         dist.all_reduce(mean, op=dist.ReduceOp.SUM)
         ingress_mean = float(mean.item()) / world
@@ -377,7 +388,8 @@ def run_ours(args, rank, world, local_rank):
                   "link_peak_kind": "measured peer copy per direction (900 nominal)",
                   "roofline_ms": roof_ms, "step_ms": step_ms, "frac_of_roofline": roof_ms / step_ms,
                   "frac_of_900": max(wire / 900.0 / 1e6, op_bytes / peak / 1e6) / step_ms, "mode": args.ep,
-                  "layout": getattr(ep, "layout", None)}
+                  "layout": getattr(ep, "layout", None), "send_once": send_once,
+                  "egress_bytes_if_every_pair_crossed": all_pairs_egress}
     clocks = sampler.stop() if rank == 0 else None
     if fused:
         roofline = {"bound": "nvlink",
@@ -819,6 +831,8 @@ def main():
     ap.add_argument("--op", default="route_dispatch", choices=["route_dispatch", "combine", "combine_add"])
     ap.add_argument("--ep-layout", default=None, choices=["packed", "separate"],
                     help="fused exchange, fp8 rows: scales after each row (one copy per pair) or in a buffer of their own")
+    ap.add_argument("--ep-every-pair", action="store_true",
+                    help="fused exchange: every pair carries its row over NVLink (no send-once / owner-side copies)")
     ap.add_argument("--ep", default="fused", choices=["fused", "nccl"],
                     help="expert-parallel exchange at N > 1: one peer-store kernel, or NCCL all-to-all + reorder")
     args = ap.parse_args()

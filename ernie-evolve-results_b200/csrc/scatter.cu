@@ -573,7 +573,10 @@ cudaError_t launch_scatter_bulk(const moe_rd_params& p, const moe_rd_buffers& b,
 cudaError_t launch_scatter_bulk_ep(const moe_rd_params& p, const void* x, const int32_t* ids,
                                    const int32_t* inverse_perm, const int32_t* offsets,
                                    const int32_t* dest_base, int world, void* const* peer_rows,
-                                   float* const* peer_scales, int32_t* status, cudaStream_t s);
+                                   float* const* peer_scales, int rank, int32_t* const* peer_copy_of,
+                                   int32_t* status, cudaStream_t s);
+cudaError_t launch_ep_replicate(void* rows, float* scales, int32_t* copy_of, const int32_t* n_rows,
+                                int64_t max_rows, int H, bool fp8, int32_t* status, cudaStream_t s);
 bool bulk_scatter_eligible(const moe_rd_params& p);
 
 size_t positions_smem(int K, int E) { return (size_t)((kTile * K + 31) / 32) * E * 2 + 16; }
@@ -719,10 +722,51 @@ extern "C" int moe_rd_ep_plan(const int32_t* kept_all, int world, int rank, int 
   return cudaGetLastError() == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
 }
 
+static int ep_scatter_impl(const moe_rd_params* p, const void* x, const int32_t* expert_ids,
+                           const int32_t* inverse_perm, const int32_t* offsets, const int32_t* dest_base,
+                           int world, void* const* peer_rows, float* const* peer_scales, int rank,
+                           int32_t* const* peer_copy_of, int32_t* status, void* stream);
+
 extern "C" int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const int32_t* expert_ids,
                                  const int32_t* inverse_perm, const int32_t* offsets,
                                  const int32_t* dest_base, int world, void* const* peer_rows,
                                  float* const* peer_scales, int32_t* status, void* stream) {
+  return ep_scatter_impl(p, x, expert_ids, inverse_perm, offsets, dest_base, world, peer_rows, peer_scales, -1,
+                         nullptr, status, stream);
+}
+
+extern "C" int moe_rd_ep_scatter_once(const moe_rd_params* p, const void* x, const int32_t* expert_ids,
+                                      const int32_t* inverse_perm, const int32_t* offsets,
+                                      const int32_t* dest_base, int world, int rank, void* const* peer_rows,
+                                      float* const* peer_scales, int32_t* const* peer_copy_of,
+                                      int32_t* status, void* stream) {
+  if (peer_copy_of == nullptr) return MOE_RD_E_NULL;
+  if (rank < 0 || rank >= world) return MOE_RD_E_SHAPE;
+  if (p != nullptr && p->scatter_impl != MOE_RD_SCATTER_BULK) return MOE_RD_E_UNSUPPORTED;
+  for (int d = 0; d < world && d < kMaxWorld; ++d)
+    if (peer_copy_of[d] == nullptr) return MOE_RD_E_NULL;
+  return ep_scatter_impl(p, x, expert_ids, inverse_perm, offsets, dest_base, world, peer_rows, peer_scales, rank,
+                         peer_copy_of, status, stream);
+}
+
+extern "C" int moe_rd_ep_replicate(const moe_rd_params* p, void* rows, float* scales, int32_t* copy_of,
+                                   const int32_t* n_rows, int64_t max_rows, int32_t* status, void* stream) {
+  if (p == nullptr || rows == nullptr || copy_of == nullptr || n_rows == nullptr || status == nullptr)
+    return MOE_RD_E_NULL;
+  const bool fp8 = p->rows_format == MOE_RD_ROWS_FP8_E4M3_B128;
+  if (max_rows < 0 || p->H % 8 != 0 || (fp8 && p->H % 512 != 0)) return MOE_RD_E_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(rows) | reinterpret_cast<uintptr_t>(scales)) & 15) return MOE_RD_E_ALIGN;
+  if (max_rows == 0) return MOE_RD_OK;
+  const cudaError_t e = launch_ep_replicate(rows, scales, copy_of, n_rows, max_rows, p->H, fp8, status,
+                                            static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) set_last_cuda_error(e);
+  return e == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
+}
+
+static int ep_scatter_impl(const moe_rd_params* p, const void* x, const int32_t* expert_ids,
+                           const int32_t* inverse_perm, const int32_t* offsets, const int32_t* dest_base,
+                           int world, void* const* peer_rows, float* const* peer_scales, int rank,
+                           int32_t* const* peer_copy_of, int32_t* status, void* stream) {
   if (p == nullptr || x == nullptr || expert_ids == nullptr || inverse_perm == nullptr ||
       offsets == nullptr || dest_base == nullptr || peer_rows == nullptr)
     return MOE_RD_E_NULL;
@@ -744,7 +788,7 @@ extern "C" int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const in
     if (status == nullptr) return MOE_RD_E_NULL;
     const cudaError_t be =
         launch_scatter_bulk_ep(*p, x, expert_ids, inverse_perm, offsets, dest_base, world, peer_rows,
-                               peer_scales, status, static_cast<cudaStream_t>(stream));
+                               peer_scales, rank, peer_copy_of, status, static_cast<cudaStream_t>(stream));
     return be == cudaSuccess ? MOE_RD_OK : MOE_RD_E_CUDA;
   }
   ScatterArgs a = {};

@@ -90,6 +90,12 @@ struct BulkArgs {
   float* peer_scales[kMaxWorld];
   int epr;
   int packed;  // 1 (expert-parallel fp8): a destination row is H bytes followed by its H/128 scales
+  // Send-once exchange: a token that has several experts on one remote rank crosses NVLink once.  Its
+  // first pair there carries the row; for every later pair the sender stores only
+  // copy_of[row of that pair] = row of the first pair (4 bytes) in the owner's memory, and the owner
+  // copies the row locally afterwards (ep_replicate_kernel).  Null pointers: every pair carries its row.
+  int rank;
+  int32_t* peer_copy_of[kMaxWorld];
 };
 
 // Destination of pair (t,k) with local row q >= 0: buffers and row to write;
@@ -111,6 +117,18 @@ __device__ __forceinline__ bool bulk_dest(const BulkArgs& a, int64_t t, int k, i
   rows = static_cast<unsigned char*>(a.peer_rows[d]);
   scales = reinterpret_cast<unsigned char*>(a.peer_scales[d]);
   row = (int64_t)db + (q - __ldg(a.offsets + e));
+  if (d != a.rank && a.peer_copy_of[d] != nullptr) {
+    // an earlier pair of this token that has a row on the same rank already carries the bytes
+    for (int j = 0; j < k; ++j) {
+      const int ej = __ldg(a.ids + (size_t)t * a.K + j);
+      if (ej / a.epr != d) continue;
+      const int qj = __ldg(a.inverse_perm + (size_t)t * a.K + j);
+      const int dbj = __ldg(a.dest_base + ej);
+      if (qj < 0 || dbj < 0) continue;
+      a.peer_copy_of[d][row] = dbj + (qj - __ldg(a.offsets + ej));
+      return false;
+    }
+  }
   return true;
 }
 
@@ -337,7 +355,8 @@ cudaError_t launch_scatter_bulk(const moe_rd_params& p, const moe_rd_buffers& b,
 cudaError_t launch_scatter_bulk_ep(const moe_rd_params& p, const void* x, const int32_t* ids,
                                    const int32_t* inverse_perm, const int32_t* offsets,
                                    const int32_t* dest_base, int world, void* const* peer_rows,
-                                   float* const* peer_scales, int32_t* status, cudaStream_t s) {
+                                   float* const* peer_scales, int rank, int32_t* const* peer_copy_of,
+                                   int32_t* status, cudaStream_t s) {
   BulkArgs a = {};
   a.x = static_cast<const uint16_t*>(x);
   a.inverse_perm = inverse_perm;
@@ -352,9 +371,79 @@ cudaError_t launch_scatter_bulk_ep(const moe_rd_params& p, const void* x, const 
   for (int d = 0; d < world; ++d) {
     a.peer_rows[d] = peer_rows[d];
     a.peer_scales[d] = peer_scales != nullptr ? peer_scales[d] : nullptr;
+    a.peer_copy_of[d] = peer_copy_of != nullptr ? peer_copy_of[d] : nullptr;
   }
+  a.rank = rank;
   a.packed = (peer_scales == nullptr && p.rows_format == MOE_RD_ROWS_FP8_E4M3_B128) ? 1 : 0;
   return launch_bulk_args(p, a, true, s);
+}
+
+// ---------------------------------------------------------------------------
+// Owner side of the send-once exchange: row r with copy_of[r] = s >= 0 did not
+// cross NVLink; it is a copy of row s of the same buffer (the same token, sent
+// for an earlier expert of this rank).  One warp per row, 16-byte vectors; the
+// mark is cleared for the next step.  Runs after the barrier that orders every
+// rank's stores.  A source row is never itself a copy (the sender marks only
+// later pairs, and names the first one that carries a row).
+// ---------------------------------------------------------------------------
+struct ReplicateArgs {
+  unsigned char* rows;
+  unsigned char* scales;   // null: bf16 rows, or scales inside the row pitch (packed)
+  int32_t* copy_of;
+  const int32_t* n_rows;   // device value: rows received in this step
+  int32_t* status;
+  int64_t max_rows;
+  uint32_t row_pitch, row_copy, scale_pitch;
+};
+
+__global__ void __launch_bounds__(256) ep_replicate_kernel(const ReplicateArgs a) {
+  pdl_sync();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (int64_t)gridDim.x * 8;
+  int64_t n = __ldg(a.n_rows);
+  n = n < 0 ? 0 : (n > a.max_rows ? a.max_rows : n);
+  for (int64_t r = warp; r < n; r += nwarps) {
+    const int src = a.copy_of[r];
+    if (src < 0) continue;
+    __syncwarp();
+    if (lane == 0) a.copy_of[r] = -1;
+    if (src >= n) {  // cannot happen with marks written by the scatter kernel of a consistent plan
+      if (lane == 0) report(a.status, 203, (int)r, src);
+      continue;
+    }
+    const uint4* s4 = reinterpret_cast<const uint4*>(a.rows + (size_t)src * a.row_pitch);
+    uint4* d4 = reinterpret_cast<uint4*>(a.rows + (size_t)r * a.row_pitch);
+    for (uint32_t v = lane; v < a.row_copy / 16; v += 32) d4[v] = s4[v];
+    if (a.scales != nullptr) {
+      const float* sf = reinterpret_cast<const float*>(a.scales + (size_t)src * a.scale_pitch);
+      float* df = reinterpret_cast<float*>(a.scales + (size_t)r * a.scale_pitch);
+      for (uint32_t v = lane; v < a.scale_pitch / 4; v += 32) df[v] = sf[v];
+    }
+  }
+}
+
+cudaError_t launch_ep_replicate(void* rows, float* scales, int32_t* copy_of, const int32_t* n_rows,
+                                int64_t max_rows, int H, bool fp8, int32_t* status, cudaStream_t s) {
+  ReplicateArgs a = {};
+  a.rows = static_cast<unsigned char*>(rows);
+  a.copy_of = copy_of;
+  a.n_rows = n_rows;
+  a.status = status;
+  a.max_rows = max_rows;
+  if (fp8 && scales == nullptr) {  // packed: H bytes + H/128 scales per row
+    a.row_pitch = a.row_copy = (uint32_t)(H + (H / 128) * 4);
+  } else {
+    a.row_pitch = a.row_copy = (uint32_t)(fp8 ? H : 2 * H);
+    a.scales = fp8 ? reinterpret_cast<unsigned char*>(scales) : nullptr;
+    a.scale_pitch = fp8 ? (uint32_t)(H / 128) * 4 : 0;
+  }
+  int64_t grid = (max_rows + 7) / 8;
+  const int64_t cap = (int64_t)device_sms() * 16;
+  if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
+  const cudaError_t e = launch_pdl(ep_replicate_kernel, dim3((unsigned)grid), dim3(256), 0, s, a);
+  count_launch();
+  return e;
 }
 
 }  // namespace moe_rd

@@ -21,7 +21,7 @@ EXPORTS = (
     "moe_rd_workspace_bytes", "moe_rd_route_dispatch", "moe_rd_route_dispatch_noalloc",
     "moe_rd_route_dispatch_timed", "moe_rd_read_status", "moe_rd_ep_unpack", "moe_rd_ep_plan", "moe_rd_combine",
     "moe_rd_combine_add_rows",
-    "moe_rd_ep_scatter", "moe_rd_ep_combine", "moe_rd_read_status_noalloc", "moe_rd_gemm_plan", "moe_rd_expert_stats",
+    "moe_rd_ep_scatter", "moe_rd_ep_scatter_once", "moe_rd_ep_replicate", "moe_rd_ep_combine", "moe_rd_read_status_noalloc", "moe_rd_gemm_plan", "moe_rd_expert_stats",
     "moe_rd_launch_count", "moe_rd_strerror", "moe_rd_last_cuda_error", "moe_rd_version",
 )
 
@@ -98,6 +98,14 @@ def lib() -> ctypes.CDLL:
                                         ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
                                         ctypes.c_void_p, ctypes.c_void_p]
         L.moe_rd_ep_scatter.restype = ctypes.c_int
+        L.moe_rd_ep_scatter_once.argtypes = [ctypes.POINTER(Params), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                             ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int,
+                                             ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
+                                             ctypes.POINTER(ctypes.c_void_p), ctypes.c_void_p, ctypes.c_void_p]
+        L.moe_rd_ep_scatter_once.restype = ctypes.c_int
+        L.moe_rd_ep_replicate.argtypes = [ctypes.POINTER(Params), ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
+                                          ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
+        L.moe_rd_ep_replicate.restype = ctypes.c_int
         L.moe_rd_combine.argtypes = [ctypes.c_int64, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, ctypes.c_void_p,
                                      ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
         L.moe_rd_combine.restype = ctypes.c_int

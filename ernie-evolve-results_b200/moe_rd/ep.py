@@ -134,13 +134,21 @@ class ExpertParallelFused:
     buffer.  "separate": rows and scales in two dense buffers (two copies per
     pair).  Both hold the same values.
 
+    ``send_once`` (default with bulk copies): a token with several experts on one
+    remote rank crosses NVLink once.  The first of its pairs there carries the
+    row; for the others the sender stores a 4-byte mark in the owner's memory
+    and, after the barrier, the owner copies the row inside its own buffer
+    (``moe_rd_ep_replicate``).  The buffers end up bit for bit the same; with
+    group-limited routing the NVLink bytes drop to a half (8 ranks) or a quarter
+    (2 ranks).  ``send_once=False``: every pair carries its row.
+
     If the rows bound for some rank exceed ``max_recv_rows``, the plan kernel
     records it (``check()`` raises) and the experts that do not fit receive
     nothing; no store or load leaves a buffer.
     """
 
     def __init__(self, session, group=None, max_recv_rows: Optional[int] = None,
-                 bulk: Optional[bool] = None, layout: Optional[str] = None):
+                 bulk: Optional[bool] = None, layout: Optional[str] = None, send_once: Optional[bool] = None):
         import torch.distributed._symmetric_memory as symm_mem
         # Whole-row bulk copies (cp.async.bulk through shared memory) measured ~7 % more NVLink
         # bandwidth than 16-byte stores; they need 16-byte aligned scale rows (H % 512 == 0).
@@ -193,6 +201,19 @@ class ExpertParallelFused:
             self.rows = (rows_u8 if self.fp8 else rows_u8.view(torch.bfloat16)).view(self.max_rows, H)
             self.scales = (self.buf[rows_bytes: rows_bytes + self.max_rows * self.nb * 4].view(torch.float32)
                            .view(self.max_rows, self.nb)) if self.fp8 else None
+        # send-once: a token with several experts on one remote rank crosses NVLink once; the owner copies
+        # the row for the later pairs locally (4-byte marks in copy_of, then moe_rd_ep_replicate)
+        if send_once and not self.bulk:
+            raise ValueError("send_once needs rows moved by bulk copies")
+        self.send_once = self.bulk if send_once is None else bool(send_once)
+        self.peer_copy_of = None
+        if self.send_once:
+            self.copy_of = symm_mem.empty(max(self.max_rows, 1), dtype=torch.int32, device=dev)
+            self.copy_of.fill_(-1)
+            self.copy_hdl = symm_mem.rendezvous(self.copy_of, self.group)
+            self.peer_copy_of = (ctypes.c_void_p * self.world)(*[int(p) for p in self.copy_hdl.buffer_ptrs])
+            torch.cuda.synchronize(dev)
+            dist.barrier(group=self.group)   # every rank's marks read -1 before anyone stores one
         self.kept_all = torch.empty((self.world, E), dtype=torch.int32, device=dev)
         self.dest_base = torch.empty(E, dtype=torch.int32, device=dev)
         self.cnt = torch.empty((self.world, self.epr), dtype=torch.int32, device=dev)
@@ -219,10 +240,23 @@ class ExpertParallelFused:
         if self.bulk:
             params = _cabi.Params.from_buffer_copy(self.sess.params)
             params.scatter_impl = _cabi.SCATTER_IMPL["bulk"]
-        _cabi.check(L.moe_rd_ep_scatter(ctypes.byref(params), ptr(x), ptr(r.expert_ids),
-                                        ptr(r.inverse_perm), ptr(offs), ptr(self.dest_base), self.world,
-                                        self.peer_rows, self.peer_scales, ptr(self.status), stream))
+        if self.send_once:
+            _cabi.check(L.moe_rd_ep_scatter_once(ctypes.byref(params), ptr(x), ptr(r.expert_ids),
+                                                 ptr(r.inverse_perm), ptr(offs), ptr(self.dest_base), self.world,
+                                                 self.rank, self.peer_rows, self.peer_scales, self.peer_copy_of,
+                                                 ptr(self.status), stream))
+        else:
+            _cabi.check(L.moe_rd_ep_scatter(ctypes.byref(params), ptr(x), ptr(r.expert_ids),
+                                            ptr(r.inverse_perm), ptr(offs), ptr(self.dest_base), self.world,
+                                            self.peer_rows, self.peer_scales, ptr(self.status), stream))
         self._barrier()  # every rank's stores are done and visible after this
+        if self.send_once:
+            # rows that did not cross NVLink: copies of an earlier row of the same token in this buffer
+            _cabi.check(L.moe_rd_ep_replicate(
+                ctypes.byref(params), ptr(self.buf), None if self.layout == "packed" or not self.fp8
+                else ctypes.c_void_p(self.scales.data_ptr()), ptr(self.copy_of),
+                ctypes.c_void_p(self.local_offsets.data_ptr() + 4 * self.epr), self.max_rows, ptr(self.status),
+                stream))
         return EPResult(self.rows, self.scales, self.local_offsets, self.cnt, -1, -1)
 
     def _barrier(self) -> None:

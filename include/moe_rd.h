@@ -250,6 +250,32 @@ int moe_rd_ep_scatter(const moe_rd_params* p, const void* x, const int32_t* expe
                       float* const* peer_scales, int32_t* status, void* stream);
 
 /*
+ * Send-once form of moe_rd_ep_scatter (bulk copies only): a token with several
+ * experts on one REMOTE rank crosses NVLink once.  The first of its pairs that
+ * has a row there carries the bytes; for every later pair the kernel stores only
+ *   peer_copy_of[d][row of that pair] = row of the first pair       (4 bytes)
+ * in the owner's memory.  After the cross-rank barrier every owner runs
+ * moe_rd_ep_replicate on its own buffer: each row r < *n_rows with
+ * copy_of[r] >= 0 is copied from that row (local HBM traffic) and the mark is
+ * reset to -1.  The buffers end up exactly as moe_rd_ep_scatter leaves them.
+ * With group-limited routing (at most 4 of 8 expert groups per token) this
+ * halves the NVLink bytes on 8 ranks and quarters them on 2.  Pairs bound for
+ * `rank` itself are written directly, as before.
+ * peer_copy_of: host array of `world` device pointers to int32 [max_rows], every
+ * element -1 before the first use (the owner's own replicate keeps it so).
+ * moe_rd_ep_replicate: rows / scales / copy_of are this rank's buffers (scales
+ * NULL for bf16 rows and for the packed fp8 layout), n_rows a device int32
+ * (local_offsets[E/world] of moe_rd_ep_plan), status an 8-word device block.
+ */
+int moe_rd_ep_scatter_once(const moe_rd_params* p, const void* x, const int32_t* expert_ids,
+                           const int32_t* inverse_perm, const int32_t* offsets,
+                           const int32_t* dest_base, int world, int rank, void* const* peer_rows,
+                           float* const* peer_scales, int32_t* const* peer_copy_of, int32_t* status,
+                           void* stream);
+int moe_rd_ep_replicate(const moe_rd_params* p, void* rows, float* scales, int32_t* copy_of,
+                        const int32_t* n_rows, int64_t max_rows, int32_t* status, void* stream);
+
+/*
  * Weighted combine, the consumer of inverse_perm and combine_weights:
  *   out[t,:] = shared[t,:] + sum_k combine_weights[t,k] * y[inverse_perm[t,k],:]
  * y [rows,H] bf16 are the expert outputs in the permuted (expert-major) order,
