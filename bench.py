@@ -344,15 +344,18 @@ def run_ours(args, rank, world, local_rank):
     nvlink = None
     if world > 1:
         # the exchange alone, and the bytes that really left this GPU
-        evx = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(5)]
+        # (median of 9, the ranks aligned before each sample: the first collective of the exchange otherwise
+        # also measures how far apart the ranks happen to be)
+        evx = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(9)]
         for s_, e_ in evx:
             flush.zero_()
             sess.run(x, w, bias)
+            dist.all_reduce(torch.zeros(1, device=dev))
             s_.record()
             ep.exchange(x) if fused else ep.exchange()
             e_.record()
         torch.cuda.synchronize()
-        ex_ms = statistics.mean(s_.elapsed_time(e_) for s_, e_ in evx)
+        ex_ms = statistics.median(s_.elapsed_time(e_) for s_, e_ in evx)
         offs = sess.offsets.cpu()
         epr = E // world
         send_once = bool(getattr(ep, "send_once", False))
