@@ -119,6 +119,15 @@ def test_exchange_of_w_ranks_on_one_device(world, fmt, layout, once):
                 np.testing.assert_array_equal(img.contiguous().view(torch.int16).numpy().view(np.uint16),
                                               ref[d]["rows"])
     if once:
+        # one mark for every kept pair beyond a token's first on a REMOTE rank, none for the rank itself
+        expected = 0
+        for r, o in enumerate(per):
+            owner = o["expert_ids"] // epr
+            kept = o["inverse_perm"] >= 0
+            for d in range(world):
+                if d != r:
+                    expected += int(np.maximum(((owner == d) & kept).sum(axis=1) - 1, 0).sum())
+        assert marks == expected, (marks, expected)
         # group-limited routing: 8 experts from at most 4 groups; with 32 experts per group a rank owns
         # 8 / world groups, so a good part of the remote pairs repeat a rank
         assert marks > 0.2 * sent_rows * (world - 1) / world, (marks, sent_rows)
