@@ -413,7 +413,23 @@ __global__ void __launch_bounds__(256) ep_replicate_kernel(const ReplicateArgs a
     }
     const uint4* s4 = reinterpret_cast<const uint4*>(a.rows + (size_t)src * a.row_pitch);
     uint4* d4 = reinterpret_cast<uint4*>(a.rows + (size_t)r * a.row_pitch);
-    for (uint32_t v = lane; v < a.row_copy / 16; v += 32) d4[v] = s4[v];
+    const uint32_t nvec = a.row_copy / 16;
+    uint32_t v = lane;
+    for (; v + 224 < nvec; v += 256) {  // eight 16-byte loads in flight per lane
+      uint4 x[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) x[i] = __ldcs(s4 + v + 32 * i);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) __stcs(d4 + v + 32 * i, x[i]);
+    }
+    for (; v + 96 < nvec; v += 128) {
+      const uint4 x0 = __ldcs(s4 + v), x1 = __ldcs(s4 + v + 32), x2 = __ldcs(s4 + v + 64), x3 = __ldcs(s4 + v + 96);
+      __stcs(d4 + v, x0);
+      __stcs(d4 + v + 32, x1);
+      __stcs(d4 + v + 64, x2);
+      __stcs(d4 + v + 96, x3);
+    }
+    for (; v < nvec; v += 32) __stcs(d4 + v, __ldcs(s4 + v));
     if (a.scales != nullptr) {
       const float* sf = reinterpret_cast<const float*>(a.scales + (size_t)src * a.scale_pitch);
       float* df = reinterpret_cast<float*>(a.scales + (size_t)r * a.scale_pitch);
