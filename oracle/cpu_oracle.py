@@ -199,6 +199,42 @@ def ep_exchange(per_rank, E, world):
     return out
 
 
+def ep_send_once_marks(per_rank, E, world, n_rows_buffer):
+    """The marks of the send-once exchange, stated from the routing results alone.
+
+    A token that has several kept pairs on one REMOTE rank sends its row there once, with the first of
+    them; every later pair is a mark ``copy_of[row of that pair] = row of the first pair`` in the owner's
+    array.  Rows are numbered as in ``ep_exchange`` (expert-major; inside an expert by source rank, then by
+    the source's slot order).  Returns one int32 array [n_rows_buffer] per owner, -1 where no mark is.
+    """
+    epr = E // world
+    kept = np.stack([np.diff(np.asarray(p["offsets"], dtype=np.int64)) for p in per_rank])  # [source, expert]
+    marks = [np.full(n_rows_buffer, -1, np.int32) for _ in range(world)]
+    for d in range(world):
+        cnt = kept[:, d * epr:(d + 1) * epr]                       # [source, local expert]
+        local_start = np.concatenate([[0], np.cumsum(cnt.sum(axis=0))])[:-1]
+        before = np.cumsum(cnt, axis=0) - cnt                      # rows of lower source ranks
+        for s in range(world):
+            if s == d:
+                continue
+            ids = np.asarray(per_rank[s]["expert_ids"], dtype=np.int64)
+            inv = np.asarray(per_rank[s]["inverse_perm"], dtype=np.int64)
+            offs = np.asarray(per_rank[s]["offsets"], dtype=np.int64)
+            for t in range(ids.shape[0]):
+                first = -1
+                for k in range(ids.shape[1]):
+                    e = ids[t, k]
+                    if e // epr != d or inv[t, k] < 0:
+                        continue
+                    le = e - d * epr
+                    row = local_start[le] + before[s, le] + (inv[t, k] - offs[e])
+                    if first < 0:
+                        first = row
+                    else:
+                        marks[d][row] = first
+    return marks
+
+
 def combine(y_u16, inverse_perm, weights, shared_u16=None):
     """out[t] = shared[t] + sum_k w[t,k] * y[inverse_perm[t,k]] (bf16 bits in, bf16 bits out)."""
     y = _c(y_u16, np.uint16)

@@ -87,6 +87,7 @@ def test_exchange_of_w_ranks_on_one_device(world, fmt, layout, once):
         if once and step == 0:
             torch.cuda.synchronize()
             marks = sum(int((c >= 0).sum()) for c in copy_of)
+            marks_seen = [c.cpu().numpy() for c in copy_of]
         for r in range(world):
             if once:
                 params = _cabi.Params.from_buffer_copy(sessions[r].params)
@@ -128,6 +129,9 @@ def test_exchange_of_w_ranks_on_one_device(world, fmt, layout, once):
                 if d != r:
                     expected += int(np.maximum(((owner == d) & kept).sum(axis=1) - 1, 0).sum())
         assert marks == expected, (marks, expected)
+        # and each mark names the row of the token's first pair on that rank
+        for got, want in zip(marks_seen, cpu_oracle.ep_send_once_marks(per, E, world, max_rows)):
+            np.testing.assert_array_equal(got, want)
         # group-limited routing: 8 experts from at most 4 groups; with 32 experts per group a rank owns
         # 8 / world groups, so a good part of the remote pairs repeat a rank
         assert marks > 0.2 * sent_rows * (world - 1) / world, (marks, sent_rows)

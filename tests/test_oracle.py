@@ -358,6 +358,26 @@ def test_residual_combine_matches_numpy_restatement():
     np.testing.assert_array_equal(got[~hit], _util.bf16_bits(out0)[~hit])
 
 
+def test_send_once_marks_on_a_hand_checked_case():
+    """2 ranks, 8 experts (0-3 on rank 0, 4-7 on rank 1), 2 tokens per rank, top-3: worked out by hand."""
+    def routed(ids):
+        ids = np.array(ids, np.int32)
+        T, K = ids.shape
+        flat = ids.flatten()
+        order = np.argsort(flat, kind="stable")
+        offs = np.concatenate([[0], np.cumsum(np.bincount(flat, minlength=8))]).astype(np.int32)
+        inv = np.empty(T * K, np.int32)
+        inv[order] = np.arange(T * K)
+        return dict(expert_ids=ids, inverse_perm=inv.reshape(T, K), offsets=offs)
+    per = [routed([[0, 4, 5], [6, 7, 1]]), routed([[0, 1, 2], [4, 3, 0]])]
+    m0, m1 = cpu_oracle.ep_send_once_marks(per, 8, 2, 8)
+    # rank 0's buffer: expert 0 rows [s0 t0 | s1 t0, s1 t1], expert 1 [s0 t1 | s1 t0], expert 2 [s1 t0], expert 3 [s1 t1]
+    # source 1, token 0 has experts 0,1,2 here: rows 1 (sent), 4 and 5 (marks -> 1); token 1 has 3 then 0: row 6 sent, row 2 marked
+    np.testing.assert_array_equal(m0, [-1, -1, 6, -1, 1, 1, -1, -1])
+    # rank 1's buffer: expert 4 [s0 t0 | s1 t1], 5 [s0 t0], 6 [s0 t1], 7 [s0 t1]; source 0: token 0 rows 0 (sent), 2; token 1 rows 3 (sent), 4
+    np.testing.assert_array_equal(m1, [-1, -1, 0, -1, 3, -1, -1, -1])
+
+
 def test_row_meta_expert_stats_and_plan_restatements():
     inv = np.array([[2, 0], [-1, 1], [3, 4]], dtype=np.int32)
     w = np.array([[0.5, 0.25], [0.125, 1.0], [2.0, 4.0]], dtype=np.float32)
