@@ -89,6 +89,28 @@ def test_residual_combine_validates_before_any_cuda_call():
         moe_rd.combine_add_rows(z, torch.zeros(4, dtype=torch.int32), torch.zeros(4), torch.zeros(1, dtype=torch.int32), z)
 
 
+def test_send_once_exchange_entries_validate_before_any_cuda_call():
+    L = _cabi.lib()
+    buf = (ctypes.c_char * 256)()
+    a16 = ctypes.c_void_p((ctypes.addressof(buf) + 15) & ~15)
+    two = (ctypes.c_void_p * 2)(a16, a16)
+    p = params(scatter_impl=_cabi.SCATTER_IMPL["bulk"], E=8)
+    common = (ctypes.byref(p), a16, a16, a16, a16, a16, 2)
+    assert L.moe_rd_ep_scatter_once(*common, 0, two, None, None, a16, None) == -1            # no mark buffers
+    assert L.moe_rd_ep_scatter_once(*common, 2, two, None, two, a16, None) == -2             # rank outside the world
+    simt = params(scatter_impl=_cabi.SCATTER_IMPL["simt"], E=8)
+    assert L.moe_rd_ep_scatter_once(ctypes.byref(simt), a16, a16, a16, a16, a16, 2, 0, two, None, two, a16,
+                                    None) == -8                                              # bulk copies only
+    assert L.moe_rd_ep_scatter_once(None, a16, a16, a16, a16, a16, 2, 0, two, None, two, a16, None) == -1
+    # owner-side copies
+    assert L.moe_rd_ep_replicate(ctypes.byref(p), None, None, a16, a16, 8, a16, None) == -1
+    assert L.moe_rd_ep_replicate(ctypes.byref(p), a16, None, a16, a16, -1, a16, None) == -2
+    fp8 = params(rows_format=_cabi.ROWS_FORMAT["fp8"], H=640)
+    assert L.moe_rd_ep_replicate(ctypes.byref(fp8), a16, None, a16, a16, 8, a16, None) == -2   # scale rows not 16-byte multiples
+    assert L.moe_rd_ep_replicate(ctypes.byref(p), ctypes.c_void_p(a16.value + 4), None, a16, a16, 8, a16, None) == -4
+    assert L.moe_rd_ep_replicate(ctypes.byref(p), a16, None, a16, a16, 0, a16, None) == 0     # nothing to do
+
+
 def test_no_cpu_path():
     x = torch.zeros(4, 64, dtype=torch.bfloat16)
     w = torch.zeros(64, 8, dtype=torch.bfloat16)
