@@ -754,6 +754,104 @@ def run_combine_add(args):
         "gpu_launches": args.steps}), flush=True)
 
 
+def run_ep_kernels(args):
+    """`--op ep_kernels --ranks W`: the expert-parallel kernels of ONE rank at full size with every rank's
+    buffers on this GPU (the kernels take plain device pointers and none waits on another, so W ranks can be
+    played in one process).  What crosses NVLink in a real run is HBM traffic here, so the figures bound the
+    kernels' own cost; it is also the one way to look at them with a profiler, which cannot attach to a
+    multi-rank run.  Times rank 0's peer-store scatter (every pair, and send-once) and the owner-side copy
+    kernel with event pairs after an L2 flush."""
+    import ctypes
+    import torch
+    from moe_rd import workloads, _cabi
+    from moe_rd.runtime import Session
+    world = args.ranks
+    spec = workloads.SPECS["c5"]
+    T, H, E, K = spec["T"], spec["H"], spec["E"], spec["K"]
+    dev = torch.device("cuda", 0)
+    L = _cabi.lib()
+    stream = ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+    ptr = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())            # noqa: E731
+    ptrs = lambda ts: (ctypes.c_void_p * len(ts))(*[t.data_ptr() for t in ts])      # noqa: E731
+    epr = E // world
+    sessions, xs = [], []
+    for r in range(world):
+        t, kw = workloads.make("c5", rank=r)
+        s = Session(T, H, E, K, device=dev, w_dtype=t["w"].dtype, scatter_impl="none", **session_kwargs(kw))
+        x = t["x"].to(dev)
+        s.run(x, t["w"].to(dev), t["bias"].to(dev))
+        sessions.append(s)
+        xs.append(x)
+    max_rows = 2 * T * K
+    pitch = H + H // 32
+    rows = [torch.zeros(max_rows * pitch, dtype=torch.uint8, device=dev) for _ in range(world)]
+    copy_of = [torch.full((max_rows,), -1, dtype=torch.int32, device=dev) for _ in range(world)]
+    status = torch.zeros(8, dtype=torch.int32, device=dev)
+    plans = [dict(dest_base=torch.empty(E, dtype=torch.int32, device=dev),
+                  cnt=torch.empty((world, epr), dtype=torch.int32, device=dev),
+                  local_offsets=torch.empty(epr + 1, dtype=torch.int32, device=dev)) for _ in range(world)]
+    kept_all = torch.stack([(s.offsets[1:] - s.offsets[:-1]) for s in sessions]).contiguous()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    times = {"scatter_every_pair": [], "scatter_send_once": [], "owner_copies": []}
+    steps = max(args.steps, 3)
+    for _ in range(steps + 1):
+        for r in range(world):
+            p = plans[r]
+            _cabi.check(L.moe_rd_ep_plan(ptr(kept_all), world, r, E, max_rows, ptr(p["dest_base"]), ptr(p["cnt"]),
+                                         ptr(p["local_offsets"]), ptr(status), stream))
+        for key in ("scatter_every_pair", "scatter_send_once"):
+            for r in range(world):
+                s = sessions[r]
+                params = _cabi.Params.from_buffer_copy(s.params)
+                params.scatter_impl = _cabi.SCATTER_IMPL["bulk"]
+                a = (ctypes.byref(params), ptr(xs[r]), ptr(s.expert_ids), ptr(s.inverse_perm), ptr(s.offsets),
+                     ptr(plans[r]["dest_base"]), world)
+                if r == 0:
+                    flush.zero_()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    e0.record()
+                if key == "scatter_send_once":
+                    _cabi.check(L.moe_rd_ep_scatter_once(*a, r, ptrs(rows), None, ptrs(copy_of), ptr(status), stream))
+                else:
+                    _cabi.check(L.moe_rd_ep_scatter(*a, ptrs(rows), None, ptr(status), stream))
+                if r == 0:
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times[key].append(e0.elapsed_time(e1))
+        for r in range(world):
+            params = _cabi.Params.from_buffer_copy(sessions[r].params)
+            n_rows = ctypes.c_void_p(plans[r]["local_offsets"].data_ptr() + 4 * epr)
+            if r == 0:
+                marks = int((copy_of[0] >= 0).sum())
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+            _cabi.check(L.moe_rd_ep_replicate(ctypes.byref(params), ptr(rows[r]), None, ptr(copy_of[r]), n_rows,
+                                              max_rows, ptr(status), stream))
+            if r == 0:
+                e1.record()
+                torch.cuda.synchronize()
+                times["owner_copies"].append(e0.elapsed_time(e1))
+    assert int(status[0]) == 0, status.tolist()
+    ms = {k: statistics.median(v[1:]) for k, v in times.items()}
+    received = int(plans[0]["local_offsets"][-1])
+    copy_bytes = 2 * marks * pitch
+    peak, kind = measured_hbm_peak()
+    print(json.dumps({
+        "metric": "ep_kernel_ms", "value": ms["scatter_send_once"] + ms["owner_copies"], "unit": "ms", "n_gpus": 1,
+        "steps": steps, "warmup": 1, "ms_per_step": ms["scatter_send_once"] + ms["owner_copies"],
+        "higher_is_better": False, "scaling": "weak", "vs_baseline": None, "dtype": "u8", "data": "synthetic",
+        "config": {"workload": f"c5, expert-parallel kernels of rank 0 of {world}, all buffers on one GPU",
+                   "tokens_per_rank": T, "hidden": H, "experts": E, "top_k": K,
+                   "l2": "flushed by a 256 MiB device write before each timed kernel"},
+        "kernel_ms": ms, "rows_received_by_rank0": received, "rows_copied_by_rank0": marks,
+        "roofline": {"bound": "hbm", "kernel": "ep_replicate_kernel", "achieved": copy_bytes / (ms["owner_copies"] * 1e-3) / 1e9,
+                     "peak": peak, "unit": "GB/s", "frac": copy_bytes / (ms["owner_copies"] * 1e-3) / 1e9 / peak,
+                     "peak_kind": f"{kind} HBM copy bandwidth", "traffic": None, "bytes_per_launch": copy_bytes,
+                     "kernel_ms": ms["owner_copies"]},
+        "gpu_launches": (steps + 1) * 4 * world}), flush=True)
+
+
 def run_combine_ep(args, rank, world, local_rank):
     """`--op combine` at N > 1: the expert-parallel combine (every rank pulls its pairs' expert outputs from
     the owning ranks over NVLink inside the combine kernel).  Routing and the dispatch run once, untimed, to
@@ -831,7 +929,8 @@ def main():
     ap.add_argument("--no-sweep", action="store_true",
                     help="skip the other_workloads / gate_vs_cublas legs of the N = 1 line")
     ap.add_argument("--scatter", default="auto", choices=["auto", "simt", "bulk"])
-    ap.add_argument("--op", default="route_dispatch", choices=["route_dispatch", "combine", "combine_add"])
+    ap.add_argument("--op", default="route_dispatch", choices=["route_dispatch", "combine", "combine_add", "ep_kernels"])
+    ap.add_argument("--ranks", type=int, default=2, choices=[2, 4, 8], help="--op ep_kernels: ranks played on one GPU")
     ap.add_argument("--ep-layout", default=None, choices=["packed", "separate"],
                     help="fused exchange, fp8 rows: scales after each row (one copy per pair) or in a buffer of their own")
     ap.add_argument("--ep-every-pair", action="store_true",
@@ -842,6 +941,10 @@ def main():
     rank, world, local_rank = env_int("RANK", 0), env_int("WORLD_SIZE", 1), env_int("LOCAL_RANK", 0)
     if world == 1 and args.gpus > 1:
         raise SystemExit("launch with torchrun for --gpus > 1 (one process per GPU)")
+    if args.op == "ep_kernels":
+        if rank == 0:
+            run_ep_kernels(args)
+        return
     if args.op == "combine_add":
         if rank == 0:
             run_combine_add(args)
