@@ -381,7 +381,7 @@ cudaError_t launch_scatter_bulk_ep(const moe_rd_params& p, const void* x, const 
 // ---------------------------------------------------------------------------
 // Owner side of the send-once exchange: row r with copy_of[r] = s >= 0 did not
 // cross NVLink; it is a copy of row s of the same buffer (the same token, sent
-// for an earlier expert of this rank).  One warp per row, 16-byte vectors; the
+// for an earlier expert of this rank).  One warp per marked row, 16-byte vectors; the
 // mark is cleared for the next step.  Runs after the barrier that orders every
 // rank's stores.  A source row is never itself a copy (the sender marks only
 // later pairs, and names the first one that carries a row).
@@ -396,45 +396,62 @@ struct ReplicateArgs {
   uint32_t row_pitch, row_copy, scale_pitch;
 };
 
+__device__ __forceinline__ void replicate_row(const ReplicateArgs& a, int64_t r, int src, int lane) {
+  const uint4* s4 = reinterpret_cast<const uint4*>(a.rows + (size_t)src * a.row_pitch);
+  uint4* d4 = reinterpret_cast<uint4*>(a.rows + (size_t)r * a.row_pitch);
+  const uint32_t nvec = a.row_copy / 16;
+  uint32_t v = lane;
+  for (; v + 224 < nvec; v += 256) {  // eight 16-byte loads in flight per lane
+    uint4 x[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x[i] = __ldcs(s4 + v + 32 * i);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) __stcs(d4 + v + 32 * i, x[i]);
+  }
+  for (; v + 96 < nvec; v += 128) {
+    const uint4 x0 = __ldcs(s4 + v), x1 = __ldcs(s4 + v + 32), x2 = __ldcs(s4 + v + 64), x3 = __ldcs(s4 + v + 96);
+    __stcs(d4 + v, x0);
+    __stcs(d4 + v + 32, x1);
+    __stcs(d4 + v + 64, x2);
+    __stcs(d4 + v + 96, x3);
+  }
+  for (; v < nvec; v += 32) __stcs(d4 + v, __ldcs(s4 + v));
+  if (a.scales != nullptr) {
+    const float* sf = reinterpret_cast<const float*>(a.scales + (size_t)src * a.scale_pitch);
+    float* df = reinterpret_cast<float*>(a.scales + (size_t)r * a.scale_pitch);
+    for (uint32_t i = lane; i < a.scale_pitch / 4; i += 32) df[i] = sf[i];
+  }
+}
+
+// A block takes 32 consecutive rows at a time: its first warp reads their marks in one coalesced load,
+// clears them and lists the marked rows in shared memory; the eight warps then share the listed rows, a
+// row per warp at a time (about a third to a half of the rows are marked, unevenly).
 __global__ void __launch_bounds__(256) ep_replicate_kernel(const ReplicateArgs a) {
+  __shared__ int s_row[32], s_src[32], s_n;
   pdl_sync();
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5), nwarps = (int64_t)gridDim.x * 8;
+  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
   int64_t n = __ldg(a.n_rows);
   n = n < 0 ? 0 : (n > a.max_rows ? a.max_rows : n);
-  for (int64_t r = warp; r < n; r += nwarps) {
-    const int src = a.copy_of[r];
-    if (src < 0) continue;
-    __syncwarp();
-    if (lane == 0) a.copy_of[r] = -1;
-    if (src >= n) {  // cannot happen with marks written by the scatter kernel of a consistent plan
-      if (lane == 0) report(a.status, 203, (int)r, src);
-      continue;
+  for (int64_t base = (int64_t)blockIdx.x * 32; base < n; base += (int64_t)gridDim.x * 32) {
+    if (w == 0) {
+      const int64_t r = base + lane;
+      int src = r < n ? a.copy_of[r] : -1;
+      if (src >= 0) a.copy_of[r] = -1;
+      if (src >= n) {  // cannot happen with marks written by the scatter kernel of a consistent plan
+        report(a.status, 203, (int)r, src);
+        src = -1;
+      }
+      const unsigned marked = __ballot_sync(kFull, src >= 0);
+      if (src >= 0) {
+        const int i = __popc(marked & ((1u << lane) - 1u));
+        s_row[i] = lane;
+        s_src[i] = src;
+      }
+      if (lane == 0) s_n = __popc(marked);
     }
-    const uint4* s4 = reinterpret_cast<const uint4*>(a.rows + (size_t)src * a.row_pitch);
-    uint4* d4 = reinterpret_cast<uint4*>(a.rows + (size_t)r * a.row_pitch);
-    const uint32_t nvec = a.row_copy / 16;
-    uint32_t v = lane;
-    for (; v + 224 < nvec; v += 256) {  // eight 16-byte loads in flight per lane
-      uint4 x[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) x[i] = __ldcs(s4 + v + 32 * i);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) __stcs(d4 + v + 32 * i, x[i]);
-    }
-    for (; v + 96 < nvec; v += 128) {
-      const uint4 x0 = __ldcs(s4 + v), x1 = __ldcs(s4 + v + 32), x2 = __ldcs(s4 + v + 64), x3 = __ldcs(s4 + v + 96);
-      __stcs(d4 + v, x0);
-      __stcs(d4 + v + 32, x1);
-      __stcs(d4 + v + 64, x2);
-      __stcs(d4 + v + 96, x3);
-    }
-    for (; v < nvec; v += 32) __stcs(d4 + v, __ldcs(s4 + v));
-    if (a.scales != nullptr) {
-      const float* sf = reinterpret_cast<const float*>(a.scales + (size_t)src * a.scale_pitch);
-      float* df = reinterpret_cast<float*>(a.scales + (size_t)r * a.scale_pitch);
-      for (uint32_t v = lane; v < a.scale_pitch / 4; v += 32) df[v] = sf[v];
-    }
+    __syncthreads();
+    for (int i = w; i < s_n; i += 8) replicate_row(a, base + s_row[i], s_src[i], lane);
+    __syncthreads();
   }
 }
 
@@ -453,7 +470,7 @@ cudaError_t launch_ep_replicate(void* rows, float* scales, int32_t* copy_of, con
     a.scales = fp8 ? reinterpret_cast<unsigned char*>(scales) : nullptr;
     a.scale_pitch = fp8 ? (uint32_t)(H / 128) * 4 : 0;
   }
-  int64_t grid = (max_rows + 7) / 8;
+  int64_t grid = (max_rows + 31) / 32;
   const int64_t cap = (int64_t)device_sms() * 16;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
